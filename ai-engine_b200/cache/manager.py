@@ -5,8 +5,8 @@ Bookkeeping (which request holds which page) is the C++ `CacheManager`
 (csrc/host/runtime.hpp); this class owns the device memory it indexes:
 
 * one pool per *group* of (run-order entry, role) whose parts ask for the same kind
-  of cache (kv heads, head size, window): `[entries, 2, pages, kv_heads, page,
-  head_dim]`, k at index 0 and v at index 1.  A page id is valid in every entry
+  of cache (kv heads, head size, window): `[entries, planes, pages, kv_heads, page,
+  head_dim]`, k at index 0 and v at index 1 (a compressed cache has one plane).  A page id is valid in every entry
   of its group, as in the reference where one allocator serves every layer's
   pool (crates/ai-engine-candle/src/paged/engine.rs:70-73); groups with
   different needs have pools and block tables of their own.
@@ -44,11 +44,11 @@ class CacheGroup:
     entries: List[Tuple[int, str]]     # (run-order index, role) that own a cache in this group
     page_size: int
     num_pages: int
-    pool: Optional[torch.Tensor] = None    # [len(entries), 2, num_pages, K, page, d]
+    pool: Optional[torch.Tensor] = None    # [len(entries), planes, num_pages, K, page, d]
 
     @property
     def bytes_per_token(self) -> int:
-        return 2 * len(self.entries) * self.request.kv_heads * self.request.head_dim
+        return self.request.planes * len(self.entries) * self.request.kv_heads * self.request.head_dim
 
 
 def group_requests(needs: Sequence[CacheNeed]):
@@ -96,7 +96,7 @@ class PagedCache:
         if allocate:
             for g in self.groups:
                 r = g.request
-                g.pool = torch.full((len(g.entries), 2, g.num_pages, r.kv_heads, g.page_size, r.head_dim),
+                g.pool = torch.full((len(g.entries), r.planes, g.num_pages, r.kv_heads, g.page_size, r.head_dim),
                                     float("nan"), dtype=dtype, device=self.device)
             for n in self.requests:
                 if n.state is not None:
@@ -135,7 +135,8 @@ class PagedCache:
         if (run_index, role) in self.where:
             g, j = self.where[run_index, role]
             grp = self.groups[g]
-            lc.k_pages, lc.v_pages = grp.pool[j, 0], grp.pool[j, 1]
+            lc.k_pages = grp.pool[j, 0]
+            lc.v_pages = grp.pool[j, 1] if grp.request.planes > 1 else None
             lc.block_table = ctx.block_tables[g]
             lc.page_size = grp.page_size
             lc.writes = self.writes[run_index, role]

@@ -6,3 +6,6 @@ from .registry import (Architecture, load_config, register_architecture,
 __all__ = ["ConfigError", "read_json", "LlamaConfig", "RopeScaling", "Architecture",
            "load_config", "register_architecture", "registered_architectures",
            "resolve_architecture"]
+from .pifutar import PifutarConfig  # noqa: E402
+
+__all__.append("PifutarConfig")

@@ -36,8 +36,11 @@ def registered_architectures():
 
 def resolve_architecture(raw: dict) -> Architecture:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, list) or not archs:
-        raise ConfigError("config.json: required key `architectures` must be a non-empty list")
+        raise ConfigError("config.json: required key `architectures` must be a non-empty list "
+                          "(or `architecture` a name)")
     for a in archs:
         if a in _ARCHITECTURES:
             return _ARCHITECTURES[a]

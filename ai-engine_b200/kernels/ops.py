@@ -550,3 +550,248 @@ def paged_attention(q, k_pages, v_pages, ctx, work, block_table, scale: float, w
             paged_attention_prefill(q, k_pages, v_pages, work.prefill_tiles, ctx.q_start, ctx.q_len,
                                     ctx.ctx_len, block_table, scale, window, ctx.err, out, cost=pre_cost)
     return out
+
+
+# ---------------------------------------------------------------------------
+# true-float32 products with strides, batches and per-tile weights
+def gemm_f32_ex(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, N: int, K: int, lda: int, ldc: int,
+                batch: int = 1, a_bs: int = 0, w_bs: int = 0, c_bs: int = 0,
+                a_rows: Optional[torch.Tensor] = None, tile_w: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m, n] = sum_k a[m, k] * w[n, k] on the CUDA cores, float32 sums in the order k = 0 .. K-1, operands
+    float32 or bfloat16 (widened), result rounded once to out's dtype.  `a`, `w`, `out` are the tensors that
+    hold the first operand of the batch at their data pointer; rows are lda / K / ldc elements apart and the
+    operands of a batch a_bs / w_bs / c_bs elements.  a_rows: row gather (-1 reads zeros).  tile_w: weight
+    index per tile of 64 rows (-1 skips the tile), the weights w_bs elements apart."""
+    for t in (a, w, out, a_rows, tile_w):
+        if t is not None and not t.is_cuda:
+            require_cuda()
+            raise KernelError("kernel operands must live on the CUDA device")
+    lib = library("gemm_f32.cu")
+    with region("gemm_f32", (N * K * w.element_size() + M * K * a.element_size() + M * N * out.element_size()) * batch,
+                2.0 * M * N * K * batch):
+        check(lib.aie_gemm_f32_ex(_p(a), c_int(dtype_code(a)), _p(w), c_int(dtype_code(w)), _p(out),
+                                  c_int(dtype_code(out)), _p(a_rows), _p(tile_w), c_int(M), c_int(N), c_int(K),
+                                  c_int(lda), c_int(ldc), c_int(batch), c_longlong(a_bs), c_longlong(w_bs),
+                                  c_longlong(c_bs), _stream()), "gemm_f32_ex")
+    return out
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Per-head projection: out[t, h, :] = w[h] . x[t, h, :] with x [T, H, K] (the last axis contiguous, any
+    strides before it), w [H, N, K], out [T, H, >= N] (written into its first N columns of the last axis)."""
+    T, H, K = x.shape
+    N = w.shape[1]
+    if w.shape != (H, N, K) or out.shape[:2] != (T, H) or out.shape[2] < N:
+        raise KernelError("head_linear: shapes do not fit")
+    if x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
+        raise KernelError("head_linear: the last axis must be contiguous")
+    return gemm_f32_ex(x, w, out, T, N, K, x.stride(0), out.stride(0), batch=H, a_bs=x.stride(1), w_bs=N * K,
+                       c_bs=out.stride(1))
+
+
+# ---------------------------------------------------------------------------
+# parts that carry state or normalise over other axes than the stream's width
+def short_conv(h: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, out_dtype: torch.dtype) -> torch.Tensor:
+    """out = h + causal convolution of h over each request's tokens, per channel.  h [T, D] float32; w [D, taps]
+    float32; state [max_seqs, taps - 1, D] float32: each request's last taps - 1 inputs, read for the first
+    tokens of its portion and replaced by the portion's last ones."""
+    _dev(h, w, state)
+    T, D = h.shape
+    taps = w.shape[1]
+    if h.dtype != torch.float32 or w.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("short_conv: inputs, taps and state are float32")
+    if w.shape[0] != D or state.shape[1:] != (max(taps - 1, 0), D):
+        raise KernelError("short_conv: shapes do not fit")
+    out = torch.empty((T, D), dtype=out_dtype, device=h.device)
+    lib = library("sequence_ops.cu")
+    with region("short_conv", _nb(h, out)):
+        check(lib.aie_short_conv(_p(h), _p(w), _p(state), _p(out), c_int(dtype_code(out)), _p(ctx.q_start),
+                                 _p(ctx.q_len), _p(ctx.slots), _p(ctx.token_req), c_int(T), c_int(D), c_int(taps),
+                                 c_int(state.shape[0]), _p(ctx.err), _stream()), "short_conv")
+    return out
+
+
+def depth_average(x: torch.Tensor, delta: Optional[torch.Tensor], history: torch.Tensor, coef: torch.Tensor,
+                  depth: int) -> None:
+    """X = x (+ delta, or the sum of its parts); history[depth] = X; x = sum_{j <= depth} coef[j] history[j],
+    in place.  x [T, D] float32; history [levels, T, D] float32; coef float32 [>= depth + 1]."""
+    _dev(x, delta, history, coef)
+    if x.dtype != torch.float32 or history.dtype != torch.float32 or coef.dtype != torch.float32:
+        raise KernelError("depth_average: stream, history and weights are float32")
+    if history.shape[1:] != x.shape or depth >= history.shape[0] or coef.shape[0] < depth + 1:
+        raise KernelError("depth_average: shapes do not fit")
+    parts, stride = 0, 0
+    if delta is not None:
+        parts, stride = (delta.shape[0], delta.stride(0)) if delta.dim() == 3 else (1, 0)
+        if delta.shape[-2:] != x.shape:
+            raise KernelError("depth_average: delta differs in shape from x")
+    lib = library("sequence_ops.cu")
+    with region("depth_average", (depth + 3) * _nb(x) + _nb(delta)):
+        check(lib.aie_depth_average(_p(x), _p(delta), c_int(dtype_code(delta) if delta is not None else 0),
+                                    c_int(parts), c_longlong(stride), _p(history), _p(coef), c_int(depth),
+                                    c_longlong(x.numel()), _stream()), "depth_average")
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """a N(z) + b N(z^2) + c N(z^3) + e per row, N = division by the root mean square; coef = (a, b, c, e)."""
+    _dev(z, coef)
+    if z.dtype != torch.float32 or coef.dtype != torch.float32 or coef.numel() != 4:
+        raise KernelError("polynorm: float32 input and four float32 coefficients")
+    T, F = z.shape
+    out = torch.empty((T, F), dtype=out_dtype, device=z.device)
+    lib = library("sequence_ops.cu")
+    with region("polynorm", _nb(z, out)):
+        check(lib.aie_polynorm(_p(z), _p(coef), _p(out), c_int(dtype_code(out)), c_int(T), c_int(F), c_float(eps),
+                               _stream()), "polynorm")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """Per (token, head): o / rms(o) (* weight) * silu(gate).  o [T, H, dv] float32; gate [T, H * dv] float32,
+    rows gate.stride(0) apart; weight [dv] float32 or None.  Returns [T, H * dv]."""
+    _dev(o, weight)
+    T, H, dv = o.shape
+    if o.dtype != torch.float32 or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape != (T, H * dv):
+        raise KernelError("head_norm_gate: shapes or dtypes do not fit")
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    lib = library("sequence_ops.cu")
+    with region("head_norm_gate", 2 * _nb(o) + _nb(out)):
+        check(lib.aie_head_norm_gate(_p(o), _p(gate), c_int(gate.stride(0)), _p(weight), _p(out),
+                                     c_int(dtype_code(out)), c_int(T), c_int(H), c_int(dv), c_float(eps), _stream()),
+              "head_norm_gate")
+    return out
+
+
+def clamped_glu(gu: torch.Tensor, F: int, limit: float, alpha: float, shift: float,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """g = min(gate, limit), u = clamp(up, +-limit): g * sigmoid(alpha g) * (u + shift).  gu [T, >= 2F] float32
+    with the gate in columns [0, F) and up in [F, 2F)."""
+    if gu.dtype != torch.float32 or gu.stride(1) != 1 or gu.shape[1] < 2 * F:
+        raise KernelError("clamped_glu: float32 [T, >= 2F] input")
+    T = gu.shape[0]
+    out = torch.empty((T, F), dtype=out_dtype, device=gu.device)
+    lib = library("sequence_ops.cu")
+    with region("clamped_glu", 2 * T * F * 4 + _nb(out)):
+        check(lib.aie_clamped_glu(_p(gu), c_int(gu.stride(0)), _p(out), c_int(dtype_code(out)), c_longlong(T),
+                                  c_int(F), c_float(limit), c_float(alpha), c_float(shift), _stream()), "clamped_glu")
+    return out
+
+
+def gated_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """sigmoid(z + bias)^(1 / tau) in float32, z [T, N] contiguous."""
+    _dev(z, bias)
+    if z.dtype != torch.float32:
+        raise KernelError("gated_decay: float32 logits")
+    out = torch.empty_like(z)
+    lib = library("sequence_ops.cu")
+    with region("gated_decay", 2 * _nb(z)):
+        check(lib.aie_gated_decay(_p(z), _p(bias), _p(out), c_longlong(z.shape[0]), c_int(z.shape[1]), c_float(tau),
+                                  _stream()), "gated_decay")
+    return out
+
+
+EXPERT_TILE = 64         # rows per tile of the grouped products
+
+
+def expert_plan(token_ids: torch.Tensor, table: torch.Tensor, experts: int, err: torch.Tensor):
+    """Group the (token, choice) pairs of a step by expert: (row_token [tiles * 64], pair_row [T * top],
+    tile_expert [tiles]); the sizes depend on T alone."""
+    _dev(token_ids, table, err)
+    T, (V, top) = token_ids.shape[0], table.shape
+    tiles = (T * top + EXPERT_TILE - 1) // EXPERT_TILE + experts
+    dev = token_ids.device
+    row_token = torch.empty(tiles * EXPERT_TILE, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(T * top, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+    lib = library("sequence_ops.cu")
+    check(lib.aie_expert_plan(_p(token_ids), _p(table), c_int(T), c_int(V), c_int(top), c_int(experts),
+                              c_int(EXPERT_TILE), c_int(tiles), _p(row_token), _p(pair_row), _p(tile_expert), _p(err),
+                              _stream()), "expert_plan")
+    return row_token, pair_row, tile_expert
+
+
+def expert_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, weight: float,
+                   shared: Optional[torch.Tensor], gate: Optional[torch.Tensor], T: int) -> torch.Tensor:
+    """out[t] = weight * sum_s y[pair_row[t top + s]] (+ shared[t] * sigmoid(gate[t])), float32 [T, D];
+    gate: a [T] float32 view (any stride)."""
+    _dev(y, pair_row, shared)
+    D = y.shape[1]
+    if y.dtype != torch.float32 or (shared is not None and (shared.dtype != torch.float32 or gate is None or
+                                                            gate.dtype != torch.float32)):
+        raise KernelError("expert_combine: float32 operands")
+    out = torch.empty((T, D), dtype=torch.float32, device=y.device)
+    lib = library("sequence_ops.cu")
+    with region("expert_combine", (top + 2) * T * D * 4):
+        check(lib.aie_expert_combine(_p(y), _p(pair_row), c_int(top), c_float(weight), _p(shared), _p(gate),
+                                     c_int(gate.stride(0) if gate is not None else 0), _p(out), c_int(T), c_int(D),
+                                     _stream()), "expert_combine")
+    return out
+
+
+def latent_prepare(proj: torch.Tensor, H: int, d: int, rot: int, rank: int, c_weight: Optional[torch.Tensor],
+                   eps: float, inv_freq: torch.Tensor, pages: torch.Tensor, ctx, block_table: torch.Tensor,
+                   q_dtype: torch.dtype, write: bool):
+    """From the fused projection [q heads (d plain | rot rotated) | latent (rank) | shared key part (rot)] of a
+    step: (q_plain [T, H, d] in q_dtype, q_full [T, H, rank + rot] float32 whose last rot columns hold the
+    rotated query parts); with `write`, the normalised latent and the rotated key part go into the tokens'
+    cache rows.  pages [num_pages, 1, P, rank + rot]."""
+    _dev(proj, c_weight, inv_freq, pages, block_table)
+    T, ld = proj.shape
+    need = H * (d + rot) + ((rank + rot) if write else 0)
+    if proj.dtype != torch.float32 or ld < need or pages.shape[1] != 1 or pages.shape[3] != rank + rot:
+        raise KernelError("latent_prepare: shapes or dtypes do not fit")
+    q_plain = torch.empty((T, H, d), dtype=q_dtype, device=proj.device)
+    q_full = torch.empty((T, H, rank + rot), dtype=torch.float32, device=proj.device)
+    lib = library("latent_attention.cu")
+    with region("latent_prepare", _nb(proj, q_plain) + T * H * rot * 4):
+        check(lib.aie_latent_prepare(_p(proj), c_int(ld), c_int(T), c_int(H), c_int(d), c_int(rot), c_int(rank),
+                                     c_int(2 * inv_freq.shape[0]), c_int(1 if write else 0), _p(c_weight),
+                                     c_float(eps), _p(inv_freq), _p(q_plain), c_int(dtype_code(q_plain)), _p(q_full),
+                                     _p(pages), c_int(dtype_code(pages)), _p(ctx.positions), _p(ctx.token_req),
+                                     _p(block_table), c_int(block_table.shape[1]), c_int(pages.shape[0]),
+                                     c_int(pages.shape[2]), _p(ctx.err), _stream()), "latent_prepare")
+    return q_plain, q_full
+
+
+def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table: torch.Tensor, rank: int,
+                     scale: float, window: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """softmax over the visible cache rows of (q_full . row) * scale, times the rows' first `rank` elements:
+    [T, H, rank].  q_full [T, H, dk] float32; pages [num_pages, 1, P, dk]."""
+    _dev(q_full, pages, block_table)
+    T, H, dk = q_full.shape
+    if q_full.dtype != torch.float32 or pages.shape[3] != dk or pages.shape[1] != 1:
+        raise KernelError("latent_attention: shapes or dtypes do not fit")
+    out = torch.empty((T, H, rank), dtype=out_dtype, device=q_full.device)
+    lib = library("latent_attention.cu")
+    with region("latent_attention", _nb(q_full, out)):
+        check(lib.aie_latent_attention(_p(q_full), _p(pages), c_int(dtype_code(pages)), _p(out),
+                                       c_int(dtype_code(out)), _p(ctx.positions), _p(ctx.token_req), _p(block_table),
+                                       c_int(block_table.shape[1]), c_int(pages.shape[0]), c_int(pages.shape[2]),
+                                       c_int(T), c_int(H), c_int(rank), c_int(dk), c_int(window), c_float(scale),
+                                       _p(ctx.err), _stream()), "latent_attention")
+    return out
+
+
+def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_tok: Optional[torch.Tensor],
+                      decay_head: Optional[torch.Tensor], q_scale: float, k_scale: float, state: torch.Tensor,
+                      ctx, H: int, d: int, dv: int) -> torch.Tensor:
+    """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens, the state
+    [max_seqs, H, d, dv] float32 read and left in each request's slot.  q, k [T, H * d] and v [T, H * dv] are
+    float32 views with one row stride; decay_tok [T, H * d] float32 (rows any stride) or decay_head [H].
+    Returns o [T, H, dv] float32."""
+    _dev(state, decay_head)
+    T = q.shape[0]
+    ld = q.stride(0)
+    if (q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k.stride(0) != ld
+            or v.stride(0) != ld or q.stride(1) != 1 or state.shape[1:] != (H, d, dv) or state.dtype != torch.float32):
+        raise KernelError("linear_recurrence: shapes or dtypes do not fit")
+    out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+    lib = library("linear_recurrence.cu")
+    with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4, 4.0 * T * H * d * dv):
+        check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
+                                        c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
+                                        c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),
+                                        _p(ctx.q_len), _p(ctx.slots), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
+                                        c_int(state.shape[0]), _p(ctx.err), _stream()), "linear_recurrence")
+    return out

@@ -1,9 +1,13 @@
 from .attention import ATTENTION_WORK, AttentionWork, GQAAttention
 from .base import (Block, BuildEnv, CacheNeed, FeedForward, KVRequest, LayerCache, Mixer, Norm, Part,
-                   PositionEncoding, StateRequest, StepPlanner)
-from .block import PreNormBlock
+                   PositionEncoding, StateRequest, StepPlanner, TokenFilter)
+from .block import DepthAveragedBlock, PreNormBlock
+from .conv import CausalShortConv
 from .embedding import LMHead, TokenEmbedding
-from .mlp import SwiGLU
+from .latent_attention import LatentAttention
+from .linear_attention import DecayLinearAttention
+from .mlp import PolyNormFF, SwiGLU
+from .moe import TableMoE
 from .model import Layer, Model, tensor_specs_of
 from .norm import RMSNorm
 from .registry import (lookup, register, register_block, register_feed_forward, register_mixer,
@@ -18,10 +22,17 @@ register("position_encoding", "rotary", RotaryEncoding)
 register("block", "prenorm", PreNormBlock)
 register("embedding", "token_embedding", TokenEmbedding)
 register("head", "lm_head", LMHead)
+register("mixer", "latent_attention", LatentAttention)
+register("mixer", "decay_linear_attention", DecayLinearAttention)
+register("feed_forward", "polynorm_ff", PolyNormFF)
+register("feed_forward", "table_moe", TableMoE)
+register("filter", "causal_short_conv", CausalShortConv)
+register("block", "prenorm_depth_average", DepthAveragedBlock)
 
 __all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv", "CacheNeed", "FeedForward",
            "KVRequest", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding", "StateRequest", "StepPlanner", "PreNormBlock", "LMHead",
            "TokenEmbedding", "SwiGLU", "Layer", "Model", "tensor_specs_of", "RMSNorm", "lookup",
            "register", "register_block", "register_feed_forward", "register_mixer",
            "register_norm", "register_position_encoding", "RotaryEncoding", "rotary_inv_freq",
-           "LayerSpec", "ModelSpec", "PartSpec", "RunStep"]
+           "LayerSpec", "ModelSpec", "PartSpec", "RunStep", "TokenFilter", "DepthAveragedBlock", "CausalShortConv",
+           "LatentAttention", "DecayLinearAttention", "PolyNormFF", "TableMoE"]

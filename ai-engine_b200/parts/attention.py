@@ -67,6 +67,8 @@ class GQAAttention(Mixer):
         pe = p.get("position_encoding")
         self.rope = env.position_encodings[pe] if pe else None
         rot = self.rope.rotation() if self.rope is not None else None
+        if self.rope is not None and getattr(self.rope, "interleaved", False):
+            raise ValueError("attention: its kernels rotate split halves; an interleaved encoding is not taken")
         if rot is not None and rot[1] > self.d:
             raise ValueError("attention: rotary width exceeds head_dim")
         self.w_qkv = self.w_o = None

@@ -31,6 +31,7 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2      # 2: keys and values; 1: one vector per token and kv head (a compressed cache)
 
 
 @dataclass(frozen=True)
@@ -71,7 +72,7 @@ class StepPlanner:
 class LayerCache:
     """What a mixer gets of the cache for one run of its layer in one step."""
     k_pages: Optional[torch.Tensor] = None       # [num_pages, kv_heads, page, head_dim]
-    v_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None       # None for a cache of one plane
     block_table: Optional[torch.Tensor] = None   # int32 [R, width], row r = request r of the batch
     page_size: int = 0
     writes: bool = True                          # False: the pages belong to another run; read only
@@ -141,6 +142,14 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenFilter(Part):
+    """Acts on each channel along a request's tokens (a short convolution): forward(h [T, hidden] float32,
+    ctx, cache) -> [T, hidden] in the compute dtype.  What it needs of earlier tokens is per-request state."""
+
+    def forward(self, h: torch.Tensor, ctx, cache: "LayerCache") -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Norm(Part):
     """forward(x, delta, rows, write_back): s = x (+ delta), stored into the
     float32 residual stream x when write_back; returns norm(s) in the compute
@@ -175,6 +184,7 @@ class Block(Part):
     for pages or state have one)."""
 
     roles: Dict[str, str] = {}
+    optional_roles: Tuple[str, ...] = ()      # roles a layer may leave out
 
     def forward(self, x, pending, ctx, caches: Dict[str, LayerCache]):
         raise NotImplementedError

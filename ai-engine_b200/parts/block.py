@@ -28,3 +28,72 @@ class PreNormBlock(Block):
         if self.ffn.adds_in_place:
             return x, self.ffn.forward(h, ctx, add_to=x)
         return x, self.ffn.forward(h, ctx)
+
+
+class DepthAveragedBlock(Block):
+    """A pre-norm block whose sublayers read their input through a filter over time, and whose result is
+    averaged with the results of all earlier layers:
+
+        h = filter(norm(x));  x = x + mixer(h);  h = filter(norm(x));  x = x + ffn(h)          -> X_(depth + 1)
+        x = sum_{j = 0 .. depth + 1} coef[j] * X_j        (X_0: the stream the first layer received)
+
+    The filters and the feed-forward (with its norm) are optional roles.  params: depth (number of layers
+    before this one), levels (layers of the model + 1).  tensors: coef [depth + 2] (absent: no averaging).
+    The streams X_j of a step live in one float32 buffer [levels, T, hidden] that the first layer makes
+    and hangs on the step context; norms hand float32 rows to the filters."""
+
+    roles = {"mixer_norm": "norm", "mixer_filter": "filter", "mixer": "mixer",
+             "ffn_norm": "norm", "ffn_filter": "filter", "ffn": "feed_forward"}
+    optional_roles = ("mixer_filter", "ffn_norm", "ffn_filter", "ffn")
+
+    def __init__(self, spec, env, parts):
+        super().__init__(spec, env)
+        self.p = parts
+        self.depth, self.levels = int(spec.params["depth"]), int(spec.params["levels"])
+        if "ffn" in parts and "ffn_norm" not in parts:
+            raise ValueError("depth-averaged block: a feed-forward needs its norm")
+        self.coef = None
+
+    def tensor_specs(self):
+        from ..weights.loader import TensorSpec
+        name = self.spec.tensors.get("coef")
+        n = self.depth + 2
+        return [TensorSpec(name, (n,), mean=1.0 / n, std=0.1 / n)] if name else []
+
+    def load(self, source):
+        name = self.spec.tensors.get("coef")
+        if name:
+            self.coef = source.get(name).float().contiguous()
+
+    def _filtered(self, role, h, ctx, caches):
+        f = self.p.get(role)
+        if f is None:
+            from ..kernels import ops
+            return ops.cast(h, self.env.dtype)
+        return f.forward(h, ctx, caches[role])
+
+    def forward(self, x, pending, ctx, caches):
+        import torch
+
+        from ..kernels import ops
+        h = self.p["mixer_norm"].forward(x, pending)
+        if self.coef is not None:
+            if self.depth == 0:
+                ctx.depth_history = torch.empty((self.levels,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+                ctx.depth_history[0].copy_(x)
+            history = ctx.depth_history
+        h = self._filtered("mixer_filter", h, ctx, caches)
+        mixer = self.p["mixer"]
+        if mixer.adds_in_place:
+            a = mixer.forward(h, ctx, caches.get("mixer"), add_to=x)
+        else:
+            a = mixer.forward(h, ctx, caches.get("mixer"))
+        ffn = self.p.get("ffn")
+        if ffn is not None:
+            h = self.p["ffn_norm"].forward(x, a)
+            h = self._filtered("ffn_filter", h, ctx, caches)
+            a = ffn.forward(h, ctx, add_to=x) if ffn.adds_in_place else ffn.forward(h, ctx)
+        if self.coef is None:
+            return x, a
+        ops.depth_average(x, a, history, self.coef, self.depth + 1)
+        return x, None

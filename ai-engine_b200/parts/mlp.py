@@ -55,3 +55,40 @@ class SwiGLU(FeedForward):
         if add_to is not None and ops.linear_add(add_to, a, self.w_down):
             return None
         return ops.linear_parts(a, self.w_down, err)   # joins the residual in float32, inside the next norm
+
+
+class PolyNormFF(FeedForward):
+    """down(act(up(x))) with act = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element, N the division of
+    a token's vector of intermediate values by its root mean square (float32).  params: hidden_size,
+    intermediate_size, eps.  tensors: up [F, hidden], down [hidden, F], act [4] = (a, b, c, e)."""
+
+    adds_in_place = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        self.eps = float(spec.params["eps"])
+        self.w_up = self.w_down = self.coef = None
+
+    def tensor_specs(self):
+        t = self.spec.tensors
+        return [TensorSpec(t["up"], (self.inter, self.hidden)), TensorSpec(t["down"], (self.hidden, self.inter)),
+                TensorSpec(t["act"], (4,), mean=0.3, std=0.1)]
+
+    def load(self, source):
+        t = self.spec.tensors
+        self.w_up, self.w_down = source.get(t["up"]), source.get(t["down"])
+        self.coef = source.get(t["act"]).float().contiguous()
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * 2 * self.inter * self.hidden
+
+    def forward(self, h, ctx, add_to=None):
+        z = ops.linear(h, self.w_up, torch.float32, ctx.err)
+        a = ops.polynorm(z, self.coef, self.eps, self.env.dtype)
+        if add_to is not None and ops.linear_add(add_to, a, self.w_down):
+            return None
+        return ops.linear_parts(a, self.w_down, ctx.err)

@@ -22,14 +22,15 @@ class Layer:
     def __init__(self, spec: LayerSpec, env: BuildEnv):
         block_cls = lookup("block", spec.block)
         roles = dict(block_cls.roles)
-        missing = [r for r in roles if r not in spec.parts]
+        missing = [r for r in roles if r not in spec.parts and r not in block_cls.optional_roles]
         unknown = [r for r in spec.parts if r not in roles]
         if missing or unknown:
             raise ValueError(f"block `{spec.block}` has the roles {sorted(roles)}: "
                              f"missing parts for {missing}, no role for {unknown}")
         self.parts: Dict[str, Part] = {
-            role: lookup(roles[role], spec.parts[role].kind)(spec.parts[role], env) for role in roles}
-        self.block = block_cls(PartSpec(spec.block), env, self.parts)
+            role: lookup(roles[role], spec.parts[role].kind)(spec.parts[role], env)
+            for role in roles if role in spec.parts}
+        self.block = block_cls(PartSpec(spec.block, dict(spec.params), dict(spec.tensors)), env, self.parts)
 
     def cache_needs(self):
         """(role, pages wanted, state wanted) of every part that asks for either."""
@@ -69,6 +70,7 @@ class Model:
         out: List[Part] = list(self.env.position_encodings.values()) + [self.embedding]
         for l in self.layers:
             out.extend(l.parts.values())
+            out.append(l.block)         # a block may have tensors of its own
         out += [self.final_norm, self.lm_head]
         return out
 

@@ -1,0 +1,87 @@
+"""A mixture of small gated feed-forwards whose experts are chosen by a table, not by a router: row `id` of the
+table [vocab, top] names the experts of a token with that id, each weighing 1 / top.  An expert is
+
+    g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit),  y = g * sigmoid(alpha g) * (u + shift),  W_down y
+
+without biases.  An optional shared expert of the same form (its own width and limit) runs for every token and
+is added, multiplied by sigmoid(w_sg . h), one number per token.
+
+A step's (token, choice) pairs are grouped by expert on the device (tiles of 64 rows, each expert's rows padded
+to whole tiles), the two products run once per tile with the tile's expert's weights, and a last kernel sums
+each token's rows in the order of its choices: no row's result depends on which other tokens are in the step.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+
+
+class TableMoE(FeedForward):
+    """params: hidden_size, vocab_size, num_experts, top, intermediate_size, limit, alpha (default 1.702), shift
+    (default 1), shared_intermediate_size (0: none), shared_limit.  tensors: table; gate, up, down as patterns with
+    `{e}` for the expert's index; shared_gate, shared_up, shared_down, shared_sg [1, hidden]."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.vocab = int(p["hidden_size"]), int(p["vocab_size"])
+        self.E, self.top, self.F = int(p["num_experts"]), int(p["top"]), int(p["intermediate_size"])
+        self.limit, self.alpha, self.shift = float(p["limit"]), float(p.get("alpha", 1.702)), float(p.get("shift", 1.0))
+        self.Fs, self.shared_limit = int(p.get("shared_intermediate_size") or 0), float(p.get("shared_limit") or 0.0)
+        self.table = self.w_gu = self.w_down = self.w_shared_in = self.w_shared_down = None
+
+    def tensor_specs(self):
+        t, D = self.spec.tensors, self.hidden
+        specs = [TensorSpec(t["table"], (self.vocab, self.top), init="distinct", high=self.E)]
+        for e in range(self.E):
+            specs += [TensorSpec(t["gate"].format(e=e), (self.F, D)), TensorSpec(t["up"].format(e=e), (self.F, D)),
+                      TensorSpec(t["down"].format(e=e), (D, self.F))]
+        if self.Fs:
+            specs += [TensorSpec(t["shared_gate"], (self.Fs, D)), TensorSpec(t["shared_up"], (self.Fs, D)),
+                      TensorSpec(t["shared_down"], (D, self.Fs)), TensorSpec(t["shared_sg"], (1, D))]
+        return specs
+
+    def load(self, source):
+        t = self.spec.tensors
+        self.table = source.get(t["table"]).to(torch.int32).contiguous()
+        gu, down = [], []
+        for e in range(self.E):
+            gu += [source.get(t["gate"].format(e=e)), source.get(t["up"].format(e=e))]
+            down.append(source.get(t["down"].format(e=e)))
+        dt = torch.float32 if any(w.dtype == torch.float32 for w in gu + down) else gu[0].dtype
+        self.w_gu = torch.stack([w.to(dt) for w in gu]).view(self.E, 2 * self.F, self.hidden).contiguous()
+        self.w_down = torch.stack([w.to(dt) for w in down]).contiguous()                  # [E, hidden, F]
+        if self.Fs:
+            ws = [source.get(t[n]) for n in ("shared_gate", "shared_up", "shared_sg")]
+            sdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+            self.w_shared_in = torch.cat([w.to(sdt) for w in ws], dim=0).contiguous()      # [2 Fs + 1, hidden]
+            self.w_shared_down = source.get(t["shared_down"])
+
+    def weight_bytes(self):
+        """What a step of many tokens reads: every expert once."""
+        return sum(w.numel() * w.element_size() for w in (self.w_gu, self.w_down, self.w_shared_in, self.w_shared_down)
+                   if w is not None)
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * 3 * self.hidden * (self.top * self.F + self.Fs)
+
+    def forward(self, h, ctx):
+        T, D, F = h.shape[0], self.hidden, self.F
+        row_token, pair_row, tile_expert = ops.expert_plan(ctx.token_ids, self.table, self.E, ctx.err)
+        rows = row_token.shape[0]
+        gu = torch.empty((rows, 2 * F), dtype=torch.float32, device=h.device)
+        ops.gemm_f32_ex(h, self.w_gu, gu, rows, 2 * F, D, D, 2 * F, w_bs=2 * F * D, a_rows=row_token,
+                        tile_w=tile_expert)
+        act = ops.clamped_glu(gu, F, self.limit, self.alpha, self.shift, self.env.dtype)
+        y = torch.empty((rows, D), dtype=torch.float32, device=h.device)
+        ops.gemm_f32_ex(act, self.w_down, y, rows, D, F, F, D, w_bs=D * F, tile_w=tile_expert)
+        shared = gate = None
+        if self.Fs:
+            sp = ops.linear(h, self.w_shared_in, torch.float32, ctx.err)
+            sa = ops.clamped_glu(sp, self.Fs, self.shared_limit, self.alpha, self.shift, self.env.dtype)
+            shared = ops.linear(sa, self.w_shared_down, torch.float32, ctx.err)
+            gate = sp[:, 2 * self.Fs]
+        return ops.expert_combine(y, pair_row, self.top, 1.0 / self.top, shared, gate, T)

@@ -10,15 +10,16 @@ POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
+FILTERS: Dict[str, type] = {}
 
 _ALL = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
         "position_encoding": POSITION_ENCODINGS, "block": BLOCKS, "embedding": EMBEDDINGS,
-        "head": HEADS}
+        "head": HEADS, "filter": FILTERS}
 
 
 def register(family: str, kind: str, cls: type) -> None:
     """Add a part class.  family: mixer | feed_forward | norm | position_encoding |
-    block | embedding | head."""
+    block | embedding | head | filter."""
     _ALL[family][kind] = cls
 
 

@@ -44,8 +44,9 @@ def rotary_inv_freq(rot_dim: int, theta: float, scaling=None) -> np.ndarray:
 
 class RotaryEncoding(PositionEncoding):
     """params: rot_dim (elements of each head that are rotated; the full head for
-    Llama), theta, scaling (None or the llama3 dict).  Holds inv_freq
-    [rot_dim / 2] float32 on the device."""
+    Llama), theta, scaling (None or the llama3 dict), layout ("halves", the default: element i turns with
+    element i + rot_dim / 2; "interleaved": element 2i with 2i + 1; a mixer reads `interleaved`).  Holds
+    inv_freq [rot_dim / 2] float32 on the device."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -55,6 +56,10 @@ class RotaryEncoding(PositionEncoding):
         self.inv_freq_host = rotary_inv_freq(self.rot_dim, float(spec.params["theta"]),
                                              spec.params.get("scaling"))
         self.inv_freq = None
+        layout = spec.params.get("layout") or "halves"
+        if layout not in ("halves", "interleaved"):
+            raise ValueError(f"rotary encoding: layout `{layout}` is not known (halves, interleaved)")
+        self.interleaved = layout == "interleaved"
 
     def load(self, source):
         self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(self.env.device)

@@ -22,9 +22,12 @@ class PartSpec:
 @dataclass
 class LayerSpec:
     """One layer: the arrangement (`block`, a registered block kind) and the parts
-    that fill its roles (for the pre-norm block: mixer_norm, mixer, ffn_norm, ffn)."""
+    that fill its roles (for the pre-norm block: mixer_norm, mixer, ffn_norm, ffn).  A block kind may
+    declare roles optional (a layer without a feed-forward leaves them out)."""
     block: str
     parts: Dict[str, PartSpec]
+    params: Dict[str, object] = field(default_factory=dict)     # the block's own constants
+    tensors: Dict[str, str] = field(default_factory=dict)       # ... and tensors (role -> tensor name)
 
 
 @dataclass

@@ -33,8 +33,9 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     """One tensor that a part wants: HF name, shape, how random weights fill it
-    (`normal`: N(0, std); `ones`: 1 + N(0, norm_std); `int`: uniform ints below
-    `high`), and `alternatives`: names that may stand in when it is absent (a
+    (`normal`: mean + N(0, std), with the tensor's own `std` if it names one; `ones`: 1 + N(0, norm_std);
+    `zeros`: N(0, norm_std), a norm weight stored as its offset from one; `int`: uniform ints below
+    `high`; `distinct`: ints below `high` that differ within each row), and `alternatives`: names that may stand in when it is absent (a
     tied head reads the embedding; an embedding absent from a tied file reads
     lm_head, crates/ai-engine-runtime/src/loader.rs:129-151)."""
     name: str
@@ -43,6 +44,9 @@ class TensorSpec:
     alternatives: Tuple[str, ...] = ()
     high: int = 0
     stored: bool = True     # False: never written by the random-weights mode (tied head)
+    mean: float = 0.0
+    std: float = 0.0        # 0: the std of the call
+    free: Tuple[int, ...] = ()   # axes whose size the file decides (`shape` there is what random weights use)
 
 
 def _storage_dtype(stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
@@ -117,10 +121,11 @@ def check_and_resolve(specs: Sequence[TensorSpec], available: Dict[str, Tuple[to
             missing.append(f"{s.name}{alt} {list(s.shape)}")
             continue
         dt, shape = available[src]
-        if tuple(shape) != tuple(s.shape):
+        if len(shape) != len(s.shape) or any(a != b for i, (a, b) in enumerate(zip(shape, s.shape))
+                                             if i not in s.free):
             wrong.append(f"{src}: stored {list(shape)}, model wants {list(s.shape)}")
-        if isinstance(dt, torch.dtype) and dt.is_floating_point == (s.init == "int"):
-            want = "integers" if s.init == "int" else "floating point (F32, F16 or BF16)"
+        if isinstance(dt, torch.dtype) and dt.is_floating_point == (s.init in ("int", "distinct")):
+            want = "integers" if s.init in ("int", "distinct") else "floating point (F32, F16 or BF16)"
             wrong_dtype.append(f"{src}: stored as {str(dt).replace('torch.', '')}, model wants {want}")
         resolved[s.name] = src
         used.add(src)

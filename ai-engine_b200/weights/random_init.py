@@ -32,13 +32,21 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu",
     if spec.init == "int":
         return torch.randint(0, max(spec.high, 1), spec.shape, generator=g, device=device,
                              dtype=torch.int32)
+    if spec.init == "distinct":
+        order = torch.rand(spec.shape[:-1] + (max(spec.high, spec.shape[-1]),), generator=g, device=device).argsort(dim=-1)
+        return order[..., :spec.shape[-1]].to(torch.int32).contiguous()
+    if spec.init == "zeros":
+        t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        if norm_std:
+            t += norm_std * torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
+        return t.to(dtype)
     if spec.init == "ones":
         t = torch.ones(spec.shape, dtype=torch.float32, device=device)
         if norm_std:
             t += norm_std * torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
         return t.to(dtype)
     t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
-    return (t * std).to(dtype)
+    return (t * (spec.std or std) + spec.mean).to(dtype)
 
 
 def random_tensors(specs: Sequence[TensorSpec], seed: int, dtype: torch.dtype, device="cpu",

@@ -112,8 +112,17 @@ template <int BN, int EPI, typename OT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                OT* __restrict__ C, int T, int N, int K, int ldc, int kb_per_split, int STAGES, int raw_parts,
-               unsigned* err, const TcRope rope) {
+               unsigned* err, const TcRope rope, const int* __restrict__ tile_w) {
     constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    // grouped rows: token tile y multiplies the weight tile_w[y] of a stack of [N, K] weights (-1: an empty tile).
+    // The list is the previous kernel's output, so it is read behind the dependency wait.
+    int w_row0 = 0;
+    if (tile_w) {
+        pdl_wait();
+        const int e = tile_w[blockIdx.y];
+        if (e < 0) return;
+        w_row0 = e * N;
+    }
     extern __shared__ unsigned char tc_raw[];
     unsigned char* bars = reinterpret_cast<unsigned char*>(((size_t)tc_raw + 1023) & ~(size_t)1023);
     unsigned char* base = bars + 1024;                    // the ring, 1024-byte aligned
@@ -161,7 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int pre = min(nkb, STAGES);
             for (int i = 0; i < pre; ++i) {
                 mbar_expect_tx(&full[i], TcSmem<BN>::stage_bytes);
-                tma_load_2d(base + i * TcSmem<BN>::stage_bytes, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+                tma_load_2d(base + i * TcSmem<BN>::stage_bytes, &map_w, &full[i], (kb_begin + i) * TC_BK, w_row0 + n0);
             }
             pdl_wait();        // the tokens are the previous kernel's output
             for (int i = 0; i < pre; ++i)
@@ -174,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 unsigned char* st = base + s * TcSmem<BN>::stage_bytes;
                 mbar_expect_tx(&full[s], TcSmem<BN>::stage_bytes);
                 const int k = (kb_begin + i) * TC_BK;
-                tma_load_2d(st, &map_w, &full[s], k, n0);
+                tma_load_2d(st, &map_w, &full[s], k, w_row0 + n0);
                 tma_load_2d(st + TC_BM * TC_BK * 2, &map_x, &full[s], k, t0);
             }
         }
@@ -335,7 +344,8 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 
 template <int BN, int EPI, typename OT>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int ldc,
-                     int splits, int raw_parts, unsigned* err, cudaStream_t st, const TcRope& rope = TcRope()) {
+                     int splits, int raw_parts, unsigned* err, cudaStream_t st, const TcRope& rope = TcRope(),
+                     const int* tile_w = nullptr) {
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     const int kbps = (kb_total + splits - 1) / splits;
     auto kern = gemm_tc_kernel<BN, EPI, OT>;
@@ -370,7 +380,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int 
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, stages, raw_parts, err, rope);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, mx, (OT*)C, T, N, K, ldc, kbps, stages, raw_parts, err, rope, tile_w);
     return (int)e;
 }
 
@@ -408,6 +418,32 @@ extern "C" int aie_gemm_tc(const void* X, const void* W, void* C, int out_dtype,
         default: return AIE_BAD_ARG;
     }
 #undef GO
+    return rc;
+}
+
+// Rows grouped by expert: X [rows, K] in tiles of `bn` rows, tile i multiplied with weight tile_w[i] of the stack
+// W [E, N, K] (-1: the tile is skipped and its rows of C are left as they are); C [rows, N].
+extern "C" int aie_gemm_tc_grouped(const void* X, const void* W, void* C, int out_dtype, int rows, int N, int K, int ldc,
+                                   int bn, int E, const int* tile_w, unsigned* err, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ((size_t)X & 15) || ((size_t)W & 15) || rows % bn || E <= 0 || !tile_w) return AIE_UNSUPPORTED;
+    if (rows / bn > 65535) return AIE_UNSUPPORTED;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, E * N, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, X, rows, K, bn);
+    if (rc) return rc;
+    if (N % TC_BM) return AIE_UNSUPPORTED;       // a weight tile must not reach into the next expert's rows
+#define GG(BNV)                                                                                                   \
+    rc = out_dtype == AIE_BF16 ? launch_tc<BNV, TC_EPI_STORE, bf16>(mw, mx, C, rows, N, K, ldc, 1, 0, err, stream, TcRope(), tile_w) \
+       : out_dtype == AIE_F32 ? launch_tc<BNV, TC_EPI_STORE, float>(mw, mx, C, rows, N, K, ldc, 1, 0, err, stream, TcRope(), tile_w) \
+       : AIE_BAD_ARG
+    switch (bn) {
+        case 64: GG(64); break;
+        case 128: GG(128); break;
+        default: return AIE_BAD_ARG;
+    }
+#undef GG
     return rc;
 }
 

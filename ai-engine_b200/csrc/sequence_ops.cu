@@ -321,3 +321,23 @@ extern "C" int aie_expert_combine(const float* y, const int* pair_row, int top, 
     expert_combine_kernel<<<T, 256, 0, st>>>(y, pair_row, top, w, shared, gate, ld_gate, out, D);
     AIE_LAUNCH_CHECK();
 }
+
+// out[r] = src[rows[r]] (zeros where rows[r] < 0): the step's rows in the order of a grouping
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows, T* __restrict__ out, int D) {
+    const int r = blockIdx.x, s = rows[r];
+    for (int c = threadIdx.x; c < D; c += blockDim.x)
+        out[(size_t)r * D + c] = s >= 0 ? src[(size_t)s * D + c] : from_f32<T>(0.f);
+}
+
+extern "C" int aie_gather_rows(const void* src, const int* rows, void* out, int dtype, int n, int D, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (D <= 0) return AIE_BAD_ARG;
+    if (dtype == AIE_F32)
+        gather_rows_kernel<float><<<n, 256, 0, st>>>((const float*)src, rows, (float*)out, D);
+    else if (dtype == AIE_BF16)
+        gather_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)src, rows, (bf16*)out, D);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}

@@ -585,6 +585,13 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
         raise KernelError("head_linear: shapes do not fit")
     if x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous():
         raise KernelError("head_linear: the last axis must be contiguous")
+    if T > TC_MAX_TOKENS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        # many tokens: the library's batched product, as for the other projections of a prompt step
+        with region("gemm_library", _nb(x, w) + T * H * N * out.element_size(), 2.0 * T * H * N * K):
+            y = torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32) if out.dtype == torch.float32 \
+                else torch.bmm(x.transpose(0, 1), w.transpose(1, 2))
+            out[:, :, :N].copy_(y.transpose(0, 1))
+        return out
     return gemm_f32_ex(x, w, out, T, N, K, x.stride(0), out.stride(0), batch=H, a_bs=x.stride(1), w_bs=N * K,
                        c_bs=out.stride(1))
 
@@ -763,8 +770,36 @@ def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table
     if q_full.dtype != torch.float32 or pages.shape[3] != dk or pages.shape[1] != 1:
         raise KernelError("latent_attention: shapes or dtypes do not fit")
     out = torch.empty((T, H, rank), dtype=out_dtype, device=q_full.device)
+    cost = (float(_nb(q_full, out)), 0.0)
+    if _profiling() and hasattr(ctx, "h_q_len"):      # cache rows read once per request, products per (query, key) pair
+        pairs = rows = 0.0
+        for n, c in zip(ctx.h_q_len.tolist(), ctx.h_ctx_len.tolist()):
+            seen = [min(c + i + 1, window) if window > 0 else c + i + 1 for i in range(n)]
+            pairs += float(sum(seen))
+            rows += float(min(c + n, (window + n) if window > 0 else c + n))
+        cost = (cost[0] + rows * dk * pages.element_size(), 2.0 * pairs * H * (dk + rank))
+    if (pages.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and rank % 64 == 0 and 64 <= rank <= 512
+            and dk % 16 == 0 and dk <= 1024):
+        # tensor cores; a step of few tokens cuts each token's keys into parts so that the grid fills the machine
+        keys = ctx.bt_width * ctx.page_size if ctx.bucketed else ctx.max_total_len
+        if window > 0:
+            keys = min(keys, window + 63)
+        ctas = T * ((H + 15) // 16)
+        splits = max(1, min(64, (keys + 63) // 64, (2 * sm_count()) // ctas))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((T, H, splits, rank), dtype=torch.float32, device=q_full.device)
+            part_ml = torch.empty((T, H, splits, 2), dtype=torch.float32, device=q_full.device)
+        lib = library("latent_attention_tc.cu")
+        with region("latent_attention_tc", *cost):
+            check(lib.aie_latent_attention_tc(_p(q_full), _p(pages), _p(out), _p(part_o), _p(part_ml), _p(ctx.positions),
+                                              _p(ctx.token_req), _p(block_table), c_int(block_table.shape[1]),
+                                              c_int(pages.shape[0]), c_int(pages.shape[2]), c_int(T), c_int(H),
+                                              c_int(rank), c_int(dk), c_int(window), c_float(scale), c_int(splits),
+                                              _p(ctx.err), _stream()), "latent_attention_tc")
+        return out
     lib = library("latent_attention.cu")
-    with region("latent_attention", _nb(q_full, out)):
+    with region("latent_attention", *cost):
         check(lib.aie_latent_attention(_p(q_full), _p(pages), c_int(dtype_code(pages)), _p(out),
                                        c_int(dtype_code(out)), _p(ctx.positions), _p(ctx.token_req), _p(block_table),
                                        c_int(block_table.shape[1]), c_int(pages.shape[0]), c_int(pages.shape[2]),
@@ -795,3 +830,35 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                                         _p(ctx.q_len), _p(ctx.slots), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
                                         c_int(state.shape[0]), _p(ctx.err), _stream()), "linear_recurrence")
     return out
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """out[r] = src[rows[r]], zeros where rows[r] < 0."""
+    _dev(src, rows)
+    out = torch.empty((rows.shape[0], src.shape[1]), dtype=src.dtype, device=src.device)
+    lib = library("sequence_ops.cu")
+    with region("gather_rows", 2 * _nb(out)):
+        check(lib.aie_gather_rows(_p(src), _p(rows), _p(out), c_int(dtype_code(src)), c_int(rows.shape[0]),
+                                  c_int(src.shape[1]), _stream()), "gather_rows")
+    return out
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_w: torch.Tensor, out_dtype: torch.dtype,
+                   err: torch.Tensor, row_src: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rows grouped in tiles of EXPERT_TILE, tile i multiplied with the weight w[tile_w[i]] of the stack w [E, N, K]
+    (tile_w[i] < 0: the tile is skipped, its output rows are undefined).  x [rows, K], or, with `row_src`
+    [rows], the rows x[row_src[r]] (zeros for -1).  bfloat16 operands whose N is a multiple of 128 and K of 8
+    take the tcgen05 kernel, everything else the float32 kernel on the CUDA cores."""
+    E, N, K = w.shape
+    rows = tile_w.shape[0] * EXPERT_TILE
+    out = torch.empty((rows, N), dtype=out_dtype, device=x.device)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and N % 128 == 0 and K % 8 == 0:
+        xs = gather_rows(x, row_src) if row_src is not None else x
+        _dev(xs, w, tile_w, err)
+        lib = library("gemm_tc.cu")
+        with region("gemm_tc_grouped", _nb(xs, w, out), 2.0 * rows * N * K):
+            check(lib.aie_gemm_tc_grouped(_p(xs), _p(w), _p(out), c_int(dtype_code(out)), c_int(rows), c_int(N),
+                                          c_int(K), c_int(N), c_int(EXPERT_TILE), c_int(E), _p(tile_w), _p(err),
+                                          _stream()), "gemm_tc_grouped")
+        return out
+    return gemm_f32_ex(x, w, out, rows, N, K, K, N, w_bs=N * K, a_rows=row_src, tile_w=tile_w)

@@ -71,13 +71,9 @@ class TableMoE(FeedForward):
     def forward(self, h, ctx):
         T, D, F = h.shape[0], self.hidden, self.F
         row_token, pair_row, tile_expert = ops.expert_plan(ctx.token_ids, self.table, self.E, ctx.err)
-        rows = row_token.shape[0]
-        gu = torch.empty((rows, 2 * F), dtype=torch.float32, device=h.device)
-        ops.gemm_f32_ex(h, self.w_gu, gu, rows, 2 * F, D, D, 2 * F, w_bs=2 * F * D, a_rows=row_token,
-                        tile_w=tile_expert)
+        gu = ops.grouped_linear(h, self.w_gu, tile_expert, torch.float32, ctx.err, row_src=row_token)
         act = ops.clamped_glu(gu, F, self.limit, self.alpha, self.shift, self.env.dtype)
-        y = torch.empty((rows, D), dtype=torch.float32, device=h.device)
-        ops.gemm_f32_ex(act, self.w_down, y, rows, D, F, F, D, w_bs=D * F, tile_w=tile_expert)
+        y = ops.grouped_linear(act, self.w_down, tile_expert, torch.float32, ctx.err)
         shared = gate = None
         if self.Fs:
             sp = ops.linear(h, self.w_shared_in, torch.float32, ctx.err)

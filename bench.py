@@ -43,6 +43,47 @@ LLAMA3_8B = dict(architectures=["LlamaForCausalLM"], hidden_size=4096, intermedi
 CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
 
 
+def pifutar_shape(width, layers=8):
+    """A Pifutar configuration with layers of the sizes real models of its kind have: heads of 128, a latent of
+    width / 4 (at least 256) with a rotated part of 64 under a window of 1,024, linear-attention heads of 128 x 128, a
+    dense first layer and experts of width / 2 (top 4 of 32) beside a shared one of `width`; the pattern of six
+    layers (latent, latent, retention, gated, two latent layers that read the second layer's cache) repeats."""
+    H = width // 128
+    latent = lambda kv_from=None: dict(type="latent_attention", mixer=dict(
+        heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=max(256, width // 4), scale=192 ** -0.5, mask=dict(size=1024),
+        rot=dict(base=500000.0, dims=64), **({} if kv_from is None else dict(kv_from=kv_from))))
+    moe = dict(kind="moe", expert=dict(ff=width // 2, limit=7.0), router=dict(experts=32, top=4),
+               shared=dict(ff=width, limit=7.0))
+    out = []
+    for i in range(layers):
+        k, base = i % 6, i - i % 6
+        if k in (0, 1):
+            l = latent()
+        elif k == 2:
+            l = dict(type="retention", mixer=dict(heads=H, dim=128, vdim=128,
+                                                  decay=[1.0 - 2.0 ** (-5 - (j % 6)) for j in range(H)]))
+        elif k == 3:
+            l = dict(type="gla", mixer=dict(heads=H, dim=128, vdim=128, tau=16.0))
+        else:
+            l = latent(base + 1)
+        l["mlp"] = dict(kind="dense", ff=3 * width) if i == 0 else moe
+        out.append(l)
+    return dict(architecture="Pifutar", vocab=32000, width=width, norm=dict(eps=1e-5), canon=dict(taps=4), layers=out)
+
+
+def llama_like(width, layers=8):
+    """The closest existing model at equal size: the same width, layers, heads of 128 (a quarter of them kv heads)
+    and a feed-forward of 3 x width, which is what a Pifutar token uses (4 experts of width / 2 + the shared one)."""
+    H = width // 128
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=width, intermediate_size=3 * width,
+                num_hidden_layers=layers, num_attention_heads=H, num_key_value_heads=max(1, H // 4), head_dim=128,
+                vocab_size=32000, max_position_embeddings=8192, rope_theta=500000.0, rms_norm_eps=1e-5,
+                tie_word_embeddings=True)
+
+
+WIDTHS = {"1k": 1024, "2k": 2048, "4k": 4096}
+
+
 def peaks():
     """Measured peaks if the driver wrote them, else the stated fallback."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -568,8 +609,11 @@ def main():
                     help="time one part only and print its numbers (for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
-    ap.add_argument("--shape", choices=["8b", "1b", "3b"], default="8b",
-                    help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape)")
+    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "llama") for w in WIDTHS],
+                    default="8b",
+                    help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape); "
+                         "pifutar-1k|2k|4k: the Pifutar design at that width, llama-1k|2k|4k: Llama at equal size beside it "
+                         "(8 layers unless --layers says otherwise)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="cached tokens per request for --profile / --only decode")
     ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
     a = ap.parse_args()
@@ -612,10 +656,15 @@ def main():
             for k, v in time_decode_attention(torch, H, K, d, lens).items():
                 print(k, json.dumps(v))
         return 0
-    cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}[a.shape] if (a.profile or a.only) else LLAMA3_8B)
-    if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":
-        cfg["num_hidden_layers"] = a.layers
-    layers = cfg["num_hidden_layers"]
+    if "-" in a.shape and (a.profile or a.only):
+        family, w = a.shape.split("-")
+        layers = a.layers if a.layers != LLAMA3_8B["num_hidden_layers"] else 8
+        cfg = (pifutar_shape if family == "pifutar" else llama_like)(WIDTHS[w], layers)
+    else:
+        cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}.get(a.shape, LLAMA3_8B) if (a.profile or a.only) else LLAMA3_8B)
+        if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":
+            cfg["num_hidden_layers"] = a.layers
+        layers = cfg["num_hidden_layers"]
     model, _ = random_model(cfg, seed=0, dtype="bf16")
     if a.profile:
         from ai_engine_b200.kernels import profile

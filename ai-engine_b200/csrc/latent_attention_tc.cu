@@ -3,7 +3,9 @@
 // cache rows, so the heads are the rows of the products: one CTA owns one query token and a group of 16 heads
 // (one m16 tile of mma.sync m16n8k16, bf16 in, float32 accumulate) and walks the token's visible keys in chunks
 // of 64 that start at multiples of 64 of the absolute key position (a row's additions depend on its position
-// only, not on how the prompt was cut or on the batch).
+// only, not on how the prompt was cut or on the batch).  A CTA of a prompt's portion takes TQ = 4 consecutive tokens
+// of one request (four warps each): they share the gathered cache rows, whose traffic from L2 bounds the kernel,
+// and differ only in their masks.
 //
 // Per chunk: the 64 cache rows are gathered page by page into shared memory by 16-byte cp.async copies (rows
 // outside the mask or the block table are zero-filled, so a probability of 0 never meets an unwritten row);
@@ -18,40 +20,53 @@
 #define LT_ROWS 16
 #define LT_THREADS 128
 
-template <int CW>      // latent columns per warp (rank = 4 CW)
-__global__ void __launch_bounds__(LT_THREADS)
+template <int CW, int TQ>      // latent columns per warp (rank = 4 CW); tokens per CTA
+__global__ void __launch_bounds__(LT_THREADS * TQ)
 latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restrict__ pages, bf16* __restrict__ out,
-                           float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ positions,
-                           const int* __restrict__ token_req, const int* __restrict__ block_table, int bt_width,
+                           float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tiles,
+                           const int* __restrict__ q_start, const int* __restrict__ q_len,
+                           const int* __restrict__ ctx_len, const int* __restrict__ block_table, int bt_width,
                            int num_pages, int P, int H, int dk, int window, float scale, int splits, unsigned* err) {
-    constexpr int RANK = 4 * CW, NT = CW / 8;
+    constexpr int RANK = 4 * CW, NT = CW / 8, THREADS = LT_THREADS * TQ;
     extern __shared__ __align__(16) unsigned char lt_raw[];
     const int SK = dk + 8;                                        // padded row: ldmatrix rows fall on different banks
-    bf16* q_s = reinterpret_cast<bf16*>(lt_raw);                  // [16][SK]
-    bf16* k_s = q_s + LT_ROWS * SK;                               // [64][SK]
-    bf16* p_s = k_s + LT_KEYS * SK;                               // [16][64 + 8]
-    float* s_s = reinterpret_cast<float*>(p_s + LT_ROWS * (LT_KEYS + 8));     // [16][64 + 1]
-    float* m_s = s_s + LT_ROWS * (LT_KEYS + 1);                   // [16] running maximum
-    float* l_s = m_s + LT_ROWS;                                   // [16] running sum
-    float* c_s = l_s + LT_ROWS;                                   // [16] correction of this chunk
+    bf16* q_all = reinterpret_cast<bf16*>(lt_raw);                // [TQ][16][SK]
+    bf16* k_s = q_all + TQ * LT_ROWS * SK;                        // [64][SK]
+    bf16* p_all = k_s + LT_KEYS * SK;                             // [TQ][16][64 + 8]
+    float* s_all = reinterpret_cast<float*>(p_all + TQ * LT_ROWS * (LT_KEYS + 8));     // [TQ][16][64 + 1]
+    float* m_all = s_all + TQ * LT_ROWS * (LT_KEYS + 1);          // [TQ][16] running maximum
+    float* l_all = m_all + TQ * LT_ROWS;                          // [TQ][16] running sum
+    float* c_all = l_all + TQ * LT_ROWS;                          // [TQ][16] correction of this chunk
 
-    const int t = blockIdx.x, h0 = blockIdx.y * LT_ROWS, part = blockIdx.z;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int pos = positions[t], row = token_req[t];
-    int lo = 0;
+    const int row = tiles[2 * blockIdx.x], off = tiles[2 * blockIdx.x + 1];
+    const int h0 = blockIdx.y * LT_ROWS, part = blockIdx.z;
+    const int tid = threadIdx.x, tq = tid / LT_THREADS, ltid = tid % LT_THREADS, warp = (tid >> 5) & 3, lane = tid & 31;
+    const int n_act = min(TQ, q_len[row] - off);                  // tokens of this CTA that exist
+    const int pos_first = ctx_len[row] + off, pos_last = pos_first + n_act - 1;
+    const int t = q_start[row] + off + tq;
+    const bool active = tq < n_act;
+    const int pos = active ? pos_first + tq : -1;                 // a token that does not exist sees no key
+    int lo = 0, lo_first = 0;
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
-    const int first_chunk = lo / LT_KEYS, n_chunks = pos / LT_KEYS - first_chunk + 1;
+    if (window > 0 && pos_first - window + 1 > 0) lo_first = pos_first - window + 1;
+    const int first_chunk = lo_first / LT_KEYS, n_chunks = pos_last / LT_KEYS - first_chunk + 1;
     const int per = (n_chunks + splits - 1) / splits;
     const int c_begin = first_chunk + part * per, c_end = min(first_chunk + n_chunks, c_begin + per);
+    bf16* q_s = q_all + tq * LT_ROWS * SK;
+    bf16* p_s = p_all + tq * LT_ROWS * (LT_KEYS + 8);
+    float* s_s = s_all + tq * LT_ROWS * (LT_KEYS + 1);
+    float* m_s = m_all + tq * LT_ROWS;
+    float* l_s = l_all + tq * LT_ROWS;
+    float* c_s = c_all + tq * LT_ROWS;
 
     // the 16 heads' queries, rounded to bfloat16 (rows past the last head are zero)
-    for (int e = tid; e < LT_ROWS * dk; e += LT_THREADS) {
+    for (int e = ltid; e < LT_ROWS * dk; e += LT_THREADS) {
         const int r = e / dk, c = e % dk;
-        q_s[r * SK + c] = __float2bfloat16_rn(h0 + r < H ? q_full[((size_t)t * H + h0 + r) * dk + c] : 0.f);
+        q_s[r * SK + c] = __float2bfloat16_rn((active && h0 + r < H) ? q_full[((size_t)t * H + h0 + r) * dk + c] : 0.f);
     }
-    if (tid < LT_ROWS) {
-        m_s[tid] = -INFINITY;
-        l_s[tid] = 0.f;
+    if (ltid < LT_ROWS) {
+        m_s[ltid] = -INFINITY;
+        l_s[ltid] = 0.f;
     }
     float acc[NT][4];
 #pragma unroll
@@ -61,9 +76,9 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
     for (int ch = c_begin; ch < c_end; ++ch) {
         const int k0 = ch * LT_KEYS;
         __syncthreads();                                          // the previous chunk's rows and probabilities are done with
-        for (int e = tid; e < LT_KEYS * pieces; e += LT_THREADS) {
+        for (int e = tid; e < LT_KEYS * pieces; e += THREADS) {
             const int j = e / pieces, c = e % pieces, kp = k0 + j;
-            bool ok = kp >= lo && kp <= pos;
+            bool ok = kp >= lo_first && kp <= pos_last;
             const bf16* src = pages;
             if (ok) {
                 const int pidx = kp / P;
@@ -103,7 +118,7 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
         __syncthreads();
         // running softmax: eight threads a row, eight keys a thread
         {
-            const int r = tid >> 3, g = tid & 7;
+            const int r = ltid >> 3, g = ltid & 7;
             float v[8], mx = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -159,6 +174,7 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
     }
     __syncthreads();
     const int ra = lane >> 2, rb = ra + 8;
+    if (!active) return;
     if (splits == 1) {
         const float ia = l_s[ra] > 0.f ? 1.0f / l_s[ra] : 0.f, ib = l_s[rb] > 0.f ? 1.0f / l_s[rb] : 0.f;
 #pragma unroll
@@ -179,10 +195,10 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
             if (h0 + rb < H)
                 *reinterpret_cast<float2*>(part_o + (((size_t)t * H + h0 + rb) * splits + part) * RANK + col) = make_float2(acc[i][2], acc[i][3]);
         }
-        if (tid < LT_ROWS && h0 + tid < H) {
-            float* ml = part_ml + (((size_t)t * H + h0 + tid) * splits + part) * 2;
-            ml[0] = m_s[tid];
-            ml[1] = l_s[tid];
+        if (ltid < LT_ROWS && h0 + ltid < H) {
+            float* ml = part_ml + (((size_t)t * H + h0 + ltid) * splits + part) * 2;
+            ml[0] = m_s[ltid];
+            ml[1] = l_s[ltid];
         }
     }
 }
@@ -207,35 +223,42 @@ __global__ void latent_join_kernel(const float* __restrict__ part_o, const float
     }
 }
 
-// q_full [T, H, dk] float32; pages [num_pages, P, dk] bfloat16; out [T, H, rank] bfloat16.  Takes rank = 64 .. 512 in
+// q_full [T, H, dk] float32; pages [num_pages, P, dk] bfloat16; out [T, H, rank] bfloat16.  tiles [n_tiles, 2] =
+// (request row, offset among the tokens it brings) of units of `tq` tokens (1 or 4).  Takes rank = 64 .. 512 in
 // steps of 64 and dk a multiple of 16 (else AIE_UNSUPPORTED: the caller takes the plain kernel).  splits > 1 needs
 // part_o [T, H, splits, rank] and part_ml [T, H, splits, 2] float32.
 extern "C" int aie_latent_attention_tc(const float* q_full, const void* pages, void* out, float* part_o, float* part_ml,
-                                       const int* positions, const int* token_req, const int* block_table, int bt_width,
+                                       const int* tiles, int n_tiles, int tq, const int* q_start, const int* q_len,
+                                       const int* ctx_len, const int* block_table, int bt_width,
                                        int num_pages, int P, int T, int H, int rank, int dk, int window, float scale,
                                        int splits, unsigned* err, cudaStream_t st) {
-    if (T <= 0) return 0;
+    if (T <= 0 || n_tiles <= 0) return 0;
     if (rank < 64 || rank > 512 || rank % 64 || dk % 16 || dk < rank || dk > 1024 || H <= 0) return AIE_UNSUPPORTED;
-    if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml))) return AIE_BAD_ARG;
+    if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml)) || (tq != 1 && tq != 4)) return AIE_BAD_ARG;
     const int SK = dk + 8;
-    const size_t smem = (size_t)(LT_ROWS + LT_KEYS) * SK * 2 + LT_ROWS * (LT_KEYS + 8) * 2 +
-                        (size_t)(LT_ROWS * (LT_KEYS + 1) + 3 * LT_ROWS) * 4;
-    dim3 grid(T, (H + LT_ROWS - 1) / LT_ROWS, splits);
+    const size_t smem = (size_t)(tq * LT_ROWS + LT_KEYS) * SK * 2 + (size_t)tq * LT_ROWS * (LT_KEYS + 8) * 2 +
+                        (size_t)tq * (LT_ROWS * (LT_KEYS + 1) + 3 * LT_ROWS) * 4;
+    if (smem > 220 * 1024) return AIE_UNSUPPORTED;
+    dim3 grid(n_tiles, (H + LT_ROWS - 1) / LT_ROWS, splits);
     if (grid.y > 65535) return AIE_UNSUPPORTED;
-#define GO(CWV)                                                                                                       \
-    case CWV: {                                                                                                       \
-        auto kern = latent_attention_tc_kernel<CWV>;                                                                  \
+#define GO1(CWV, TQV)                                                                                                 \
+    {                                                                                                                 \
+        auto kern = latent_attention_tc_kernel<CWV, TQV>;                                                             \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                           \
-        kern<<<grid, LT_THREADS, smem, st>>>(q_full, (const bf16*)pages, (bf16*)out, part_o, part_ml, positions,      \
-                                             token_req, block_table, bt_width, num_pages, P, H, dk, window, scale,    \
-                                             splits, err);                                                            \
-        break;                                                                                                        \
+        kern<<<grid, LT_THREADS * TQV, smem, st>>>(q_full, (const bf16*)pages, (bf16*)out, part_o, part_ml, tiles,    \
+                                                   q_start, q_len, ctx_len, block_table, bt_width, num_pages, P, H,   \
+                                                   dk, window, scale, splits, err);                                   \
     }
+#define GO(CWV)                                                                                                       \
+    case CWV:                                                                                                         \
+        if (tq == 1) GO1(CWV, 1) else GO1(CWV, 4)                                                                     \
+        break;
     switch (rank / 4) {
         GO(16) GO(32) GO(48) GO(64) GO(80) GO(96) GO(112) GO(128)
         default: return AIE_UNSUPPORTED;
     }
 #undef GO
+#undef GO1
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1) latent_join_kernel<<<T * H, 128, 0, st>>>(part_o, part_ml, (bf16*)out, splits, rank);

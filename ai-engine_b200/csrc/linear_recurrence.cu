@@ -8,26 +8,36 @@
 // head); `lanes` threads share a column, each with RPT consecutive rows of S in registers, and a token costs
 // each thread 2 RPT multiply-adds and a shuffle reduction over its column's lanes.  Tokens of a portion run
 // in order, so a portion of any length continues where the previous step left the state, and a request's
-// result does not depend on what else is in the batch.
+// result does not depend on what else is in the batch.  The eight warps of a block belong to one (request, head):
+// they stage the queries, keys and decays of up to sixteen tokens at a time in shared memory with coalesced
+// loads and then walk those tokens from there, so a token does not cost a round trip to memory.
 #include "common.cuh"
 
+#define LR_WARPS 8
+#define LR_TOKENS 16        // most tokens staged at a time
+#define LR_THREADS (LR_WARPS * 32)
+
 template <int RPT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(LR_THREADS)
 linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld,
                          const float* __restrict__ decay_tok, int ld_decay, const float* __restrict__ decay_head,
                          float q_scale, float k_scale, float* __restrict__ state, float* __restrict__ out,
                          const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ slots,
-                         int R, int H, int d, int dv, int lanes, int groups, int max_slots, int vec, unsigned* err) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= R * H * groups) return;
-    const int cg = warp % groups, h = (warp / groups) % H, r = warp / (groups * H);
+                         int H, int d, int dv, int lanes, int groups, int TT, int max_slots, int vec, int vec4, unsigned* err) {
+    extern __shared__ __align__(16) float lr_sm[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bg = blockIdx.x % groups, h = (blockIdx.x / groups) % H, r = blockIdx.x / (groups * H);
     const int slot = slots[r];
     if (slot < 0 || slot >= max_slots) {
-        if (lane == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
+        if (tid == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
         return;
     }
-    const int cols = 32 / lanes;
-    const int g = lane % lanes, col = cg * cols + lane / lanes;
+    const int cols = 32 / lanes, CB = LR_WARPS * cols;            // columns a warp / a block owns
+    float* q_s = lr_sm;                                           // [TT][d]
+    float* k_s = q_s + TT * d;
+    float* a_s = k_s + TT * d;                                    // only with per-token decays
+    float* v_s = decay_tok ? a_s + TT * d : a_s;                  // [TT][CB]
+    const int g = lane % lanes, cb = warp * cols + lane / lanes, col = bg * CB + cb;
     const int row0 = g * RPT;
     const bool col_ok = col < dv;
     float S[RPT];
@@ -36,42 +46,80 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     for (int i = 0; i < RPT; ++i) S[i] = (col_ok && row0 + i < d) ? sp[(size_t)(row0 + i) * dv] : 0.f;
     const float dh = decay_head ? decay_head[h] : 1.f;
     const int a = q_start[r], n = q_len[r];
-    for (int t = a; t < a + n; ++t) {
-        const float* qr = q + (size_t)t * ld + h * d + row0;
-        const float* kr = k + (size_t)t * ld + h * d + row0;
-        const float* ar = decay_tok ? decay_tok + (size_t)t * ld_decay + h * d + row0 : nullptr;
-        const float vv = col_ok ? v[(size_t)t * ld + h * dv + col] * k_scale : 0.f;
-        float o = 0.f;
-        if (vec) {
-#pragma unroll
-            for (int i = 0; i < RPT; i += 4) {
-                if (row0 + i < d) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
-                    const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
-                    float4 a4 = make_float4(dh, dh, dh, dh);
-                    if (ar) a4 = *reinterpret_cast<const float4*>(ar + i);
-                    S[i] = fmaf(a4.x, S[i], k4.x * vv);
-                    S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
-                    S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * vv);
-                    S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * vv);
-                    o = fmaf(S[i], q4.x, o);
-                    o = fmaf(S[i + 1], q4.y, o);
-                    o = fmaf(S[i + 2], q4.z, o);
-                    o = fmaf(S[i + 3], q4.w, o);
+    for (int t0 = 0; t0 < n; t0 += TT) {
+        const int nt = min(TT, n - t0);
+        __syncthreads();                                          // the previous tokens are done with
+        for (int tok = warp; tok < nt; tok += LR_WARPS) {          // a warp stages a token's rows
+            const size_t at = (size_t)(a + t0 + tok) * ld + h * d;
+            const size_t at_a = (size_t)(a + t0 + tok) * ld_decay + h * d;
+            if (vec4) {
+                for (int c = lane * 4; c < d; c += 128) {
+                    *reinterpret_cast<float4*>(q_s + tok * d + c) = *reinterpret_cast<const float4*>(q + at + c);
+                    *reinterpret_cast<float4*>(k_s + tok * d + c) = *reinterpret_cast<const float4*>(k + at + c);
+                    if (decay_tok) *reinterpret_cast<float4*>(a_s + tok * d + c) = *reinterpret_cast<const float4*>(decay_tok + at_a + c);
+                }
+            } else {
+                for (int c = lane; c < d; c += 32) {
+                    q_s[tok * d + c] = q[at + c];
+                    k_s[tok * d + c] = k[at + c];
+                    if (decay_tok) a_s[tok * d + c] = decay_tok[at_a + c];
                 }
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                if (row0 + i < d) {
-                    const float al = ar ? ar[i] : dh;
-                    S[i] = fmaf(al, S[i], kr[i] * vv);
-                    o = fmaf(S[i], qr[i], o);
-                }
-            }
+            for (int c = lane; c < CB; c += 32)
+                v_s[tok * CB + c] = bg * CB + c < dv ? v[(size_t)(a + t0 + tok) * ld + h * dv + bg * CB + c] * k_scale : 0.f;
         }
-        for (int off = lanes >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-        if (g == 0 && col_ok) out[((size_t)t * H + h) * dv + col] = o * q_scale;
+        __syncthreads();
+        // the staged tokens' updates first, then their reductions over the column's lanes side by side (sixteen
+        // independent chains of shuffles instead of one after each token)
+        float oacc[LR_TOKENS];
+#pragma unroll
+        for (int tok = 0; tok < LR_TOKENS; ++tok) {
+            oacc[tok] = 0.f;
+            if (tok >= nt) continue;
+            const float* qr = q_s + tok * d + row0;
+            const float* kr = k_s + tok * d + row0;
+            const float* ar = decay_tok ? a_s + tok * d + row0 : nullptr;
+            const float vv = v_s[tok * CB + cb];
+            float o = 0.f, o2 = 0.f;                               // two chains of additions
+            if (vec) {
+#pragma unroll
+                for (int i = 0; i < RPT; i += 4) {
+                    if (row0 + i < d) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+                        const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+                        float4 a4 = make_float4(dh, dh, dh, dh);
+                        if (ar) a4 = *reinterpret_cast<const float4*>(ar + i);
+                        S[i] = fmaf(a4.x, S[i], k4.x * vv);
+                        S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
+                        S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * vv);
+                        S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * vv);
+                        o = fmaf(S[i], q4.x, o);
+                        o = fmaf(S[i + 1], q4.y, o);
+                        o2 = fmaf(S[i + 2], q4.z, o2);
+                        o2 = fmaf(S[i + 3], q4.w, o2);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < RPT; ++i) {
+                    if (row0 + i < d) {
+                        const float al = ar ? ar[i] : dh;
+                        S[i] = fmaf(al, S[i], kr[i] * vv);
+                        o = fmaf(S[i], qr[i], o);
+                    }
+                }
+            }
+            oacc[tok] = o + o2;
+        }
+        for (int off = lanes >> 1; off > 0; off >>= 1) {
+#pragma unroll
+            for (int tok = 0; tok < LR_TOKENS; ++tok) oacc[tok] += __shfl_xor_sync(0xffffffffu, oacc[tok], off);
+        }
+        if (g == 0 && col_ok) {
+#pragma unroll
+            for (int tok = 0; tok < LR_TOKENS; ++tok)
+                if (tok < nt) out[((size_t)(a + t0 + tok) * H + h) * dv + col] = oacc[tok] * q_scale;
+        }
     }
     if (col_ok) {
 #pragma unroll
@@ -85,24 +133,36 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
 // k_scale, the output by q_scale (both 1 or d^-1/2).  state [max_slots, H, d, dv]; out [T, H, dv].
 extern "C" int aie_linear_recurrence(const float* q, const float* k, const float* v, int ld, const float* decay_tok,
                                      int ld_decay, const float* decay_head, float q_scale, float k_scale, float* state,
-                                     float* out, const int* q_start, const int* q_len, const int* slots, int R, int H,
-                                     int d, int dv, int max_slots, unsigned* err, cudaStream_t st) {
+                                     float* out, const int* q_start, const int* q_len, const int* slots, int T, int R,
+                                     int H, int d, int dv, int max_slots, unsigned* err, cudaStream_t st) {
     if (R <= 0) return 0;
     if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head)) return AIE_BAD_ARG;
     if (d > 1024) return AIE_UNSUPPORTED;
-    const int rpt = d <= 32 ? 8 : (d <= 128 ? 16 : 32);
+    // A step of single tokens is bound by reading and writing the states: many rows a thread, so that a warp's
+    // accesses to a row of the state are wide.  A step of prompt portions is bound by the chain of dependent
+    // updates token after token: few rows a thread, so that many warps hide one another's latency.
+    int rpt = d <= 32 ? 8 : (d <= 128 ? 16 : 32);
+    if (T >= 8 * R) rpt = d <= 128 ? 4 : (d <= 256 ? 8 : (d <= 512 ? 16 : 32));
     int lanes = 1;
     while (lanes * rpt < d) lanes <<= 1;
-    const int cols = 32 / lanes, groups = (dv + cols - 1) / cols;
-    const long long warps = (long long)R * H * groups;
-    const unsigned blocks = (unsigned)((warps + 3) / 4);
-    const int vec = (d % 4 == 0 && ld % 4 == 0 && (!decay_tok || ld_decay % 4 == 0) && !((size_t)q & 15) &&
-                     !((size_t)k & 15) && (!decay_tok || !((size_t)decay_tok & 15))) ? 1 : 0;
+    const int cols = 32 / lanes, CB = LR_WARPS * cols, groups = (dv + CB - 1) / CB;
+    const long long blocks = (long long)R * H * groups;
+    if (blocks > 0x7fffffffLL) return AIE_UNSUPPORTED;
+    int TT = 3072 / d;      // at most 36 KB of staged queries, keys and decays
+    TT = TT < 1 ? 1 : (TT > LR_TOKENS ? LR_TOKENS : TT);
+    const size_t smem = ((size_t)TT * d * (decay_tok ? 3 : 2) + (size_t)TT * CB) * sizeof(float);
+    // rows of the staged tokens are read as float4: the head's width and every thread's first row are multiples of 4
+    const int vec = d % 4 == 0 ? 1 : 0;
+    // ... and the rows in memory too when the row strides and base addresses allow 16-byte loads
+    const int vec4 = (vec && ld % 4 == 0 && !((size_t)q & 15) && !((size_t)k & 15) &&
+                      (!decay_tok || (ld_decay % 4 == 0 && !((size_t)decay_tok & 15)))) ? 1 : 0;
 #define GO(N)                                                                                                       \
-    linear_recurrence_kernel<N><<<blocks, 128, 0, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head, q_scale, k_scale, \
-                                                        state, out, q_start, q_len, slots, R, H, d, dv, lanes, groups, \
-                                                        max_slots, vec, err)
-    if (rpt == 8) GO(8);
+    linear_recurrence_kernel<N><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
+                                                                     q_scale, k_scale, state, out, q_start, q_len,  \
+                                                                     slots, H, d, dv, lanes, groups, TT, max_slots, \
+                                                                     vec, vec4, err)
+    if (rpt == 4) GO(4);
+    else if (rpt == 8) GO(8);
     else if (rpt == 16) GO(16);
     else GO(32);
 #undef GO

@@ -762,9 +762,11 @@ def latent_prepare(proj: torch.Tensor, H: int, d: int, rot: int, rank: int, c_we
 
 
 def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table: torch.Tensor, rank: int,
-                     scale: float, window: int, out_dtype: torch.dtype) -> torch.Tensor:
+                     scale: float, window: int, out_dtype: torch.dtype, work=None) -> torch.Tensor:
     """softmax over the visible cache rows of (q_full . row) * scale, times the rows' first `rank` elements:
-    [T, H, rank].  q_full [T, H, dk] float32; pages [num_pages, 1, P, dk]."""
+    [T, H, rank].  q_full [T, H, dk] float32; pages [num_pages, 1, P, dk].  `work`: the step's units of tokens
+    (`tiles` [n, 2], `tq`) for the tensor-core kernel, which bfloat16 takes when the sizes fit (a latent of
+    64 .. 512 in steps of 64, rows a multiple of 16); everything else takes the plain kernel."""
     _dev(q_full, pages, block_table)
     T, H, dk = q_full.shape
     if q_full.dtype != torch.float32 or pages.shape[3] != dk or pages.shape[1] != 1:
@@ -778,13 +780,14 @@ def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table
             pairs += float(sum(seen))
             rows += float(min(c + n, (window + n) if window > 0 else c + n))
         cost = (cost[0] + rows * dk * pages.element_size(), 2.0 * pairs * H * (dk + rank))
-    if (pages.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and rank % 64 == 0 and 64 <= rank <= 512
-            and dk % 16 == 0 and dk <= 1024):
+    if (work is not None and pages.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and rank % 64 == 0
+            and 64 <= rank <= 512 and dk % 16 == 0 and dk <= 1024
+            and (work.tq * 16 + 64) * (dk + 8) * 2 + work.tq * 7000 <= 220 * 1024):
         # tensor cores; a step of few tokens cuts each token's keys into parts so that the grid fills the machine
         keys = ctx.bt_width * ctx.page_size if ctx.bucketed else ctx.max_total_len
         if window > 0:
             keys = min(keys, window + 63)
-        ctas = T * ((H + 15) // 16)
+        ctas = work.tiles.shape[0] * ((H + 15) // 16)
         splits = max(1, min(64, (keys + 63) // 64, (2 * sm_count()) // ctas))
         part_o = part_ml = None
         if splits > 1:
@@ -792,8 +795,9 @@ def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table
             part_ml = torch.empty((T, H, splits, 2), dtype=torch.float32, device=q_full.device)
         lib = library("latent_attention_tc.cu")
         with region("latent_attention_tc", *cost):
-            check(lib.aie_latent_attention_tc(_p(q_full), _p(pages), _p(out), _p(part_o), _p(part_ml), _p(ctx.positions),
-                                              _p(ctx.token_req), _p(block_table), c_int(block_table.shape[1]),
+            check(lib.aie_latent_attention_tc(_p(q_full), _p(pages), _p(out), _p(part_o), _p(part_ml), _p(work.tiles),
+                                              c_int(work.tiles.shape[0]), c_int(work.tq), _p(ctx.q_start),
+                                              _p(ctx.q_len), _p(ctx.ctx_len), _p(block_table), c_int(block_table.shape[1]),
                                               c_int(pages.shape[0]), c_int(pages.shape[2]), c_int(T), c_int(H),
                                               c_int(rank), c_int(dk), c_int(window), c_float(scale), c_int(splits),
                                               _p(ctx.err), _stream()), "latent_attention_tc")
@@ -827,7 +831,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
         check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
                                         c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
                                         c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),
-                                        _p(ctx.q_len), _p(ctx.slots), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
+                                        _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
                                         c_int(state.shape[0]), _p(ctx.err), _stream()), "linear_recurrence")
     return out
 

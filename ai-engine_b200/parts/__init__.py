@@ -4,7 +4,7 @@ from .base import (Block, BuildEnv, CacheNeed, FeedForward, KVRequest, LayerCach
 from .block import DepthAveragedBlock, PreNormBlock
 from .conv import CausalShortConv
 from .embedding import LMHead, TokenEmbedding
-from .latent_attention import LatentAttention
+from .latent_attention import LATENT_WORK, LatentAttention, LatentWork
 from .linear_attention import DecayLinearAttention
 from .mlp import PolyNormFF, SwiGLU
 from .moe import TableMoE

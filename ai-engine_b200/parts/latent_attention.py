@@ -15,11 +15,28 @@ nothing; the run order names the layer whose rows it reads.
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import KVRequest, Mixer
+from .base import KVRequest, Mixer, StepPlanner
+
+
+class LatentWork(StepPlanner):
+    """The work list of the tensor-core kernel: `tiles` [n, 2] = (request row, offset among the tokens it brings)
+    of units of `tq` consecutive tokens of one request, which share the cache rows they gather.  A step in which
+    every request brings one token has units of one token, all others units of four."""
+
+    key = "latent"
+
+    def plan(self, ctx):
+        tq = 1 if ctx.max_q_len <= 1 else 4
+        tiles = [(r, off) for r, n in enumerate(ctx.h_q_len.tolist()) for off in range(0, n, tq)]
+        return dict(tiles=np.asarray(tiles, dtype=np.int32).reshape(-1, 2)), dict(tq=tq)
+
+
+LATENT_WORK = LatentWork()
 
 
 class LatentAttention(Mixer):
@@ -89,6 +106,9 @@ class LatentAttention(Mixer):
     def cache_request(self):
         return KVRequest(1, self.rank + self.rot, self.cache_window, planes=1)
 
+    def step_planner(self):
+        return LATENT_WORK
+
     def forward(self, h, ctx, cache, add_to=None):
         T = h.shape[0]
         rot = self.rope.rotation() if self.rope is not None else None
@@ -99,7 +119,7 @@ class LatentAttention(Mixer):
                                              write=cache.writes and not self.shares_cache)
         ops.head_linear(q_plain, self.w_ukT, q_full)
         mixed = ops.latent_attention(q_full, cache.k_pages, ctx, cache.block_table, self.rank, self.scale,
-                                     self.window, self.env.dtype)
+                                     self.window, self.env.dtype, ctx.plan(LATENT_WORK))
         a = torch.empty((T, self.H, self.dv), dtype=self.env.dtype, device=h.device)
         ops.head_linear(mixed, self.w_uv, a)
         a = a.view(T, self.H * self.dv)

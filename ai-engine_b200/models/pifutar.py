@@ -80,7 +80,10 @@ def build_pifutar_spec(cfg: PifutarConfig) -> ModelSpec:
     return ModelSpec(
         hidden_size=D, vocab_size=V, max_position=cfg.max_position_embeddings, embedding=embedding, layers=layers,
         order=order, final_norm=PartSpec("rmsnorm", dict(size=D, eps=eps, offset=1.0), dict(weight="final.norm")),
-        lm_head=head, position_encodings=encodings, eos_token_ids=cfg.eos_token_ids)
+        lm_head=head, position_encodings=encodings, eos_token_ids=cfg.eos_token_ids,
+        # a layer without a feed-forward has no use for a second norm or convolution; a file may still hold them
+        ignored_tensors=tuple(f"l{i}.{n}" for i, l in enumerate(cfg.layers) if l.mlp is None
+                              for n in ("norm2", "canon2")))
 
 
 register_architecture(PifutarConfig.ARCHITECTURE, PifutarConfig, build_pifutar_spec)

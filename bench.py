@@ -45,12 +45,12 @@ CONTEXT, PROMPT_LEN, PREFILL_TOKENS, PAGE = 8192, 1024, 2048, 16
 
 def pifutar_shape(width, layers=8):
     """A Pifutar configuration with layers of the sizes real models of its kind have: heads of 128, a latent of
-    width / 4 (at least 256) with a rotated part of 64 under a window of 1,024, linear-attention heads of 128 x 128, a
+    width / 4 (256 to 512) with a rotated part of 64 under a window of 1,024, linear-attention heads of 128 x 128, a
     dense first layer and experts of width / 2 (top 4 of 32) beside a shared one of `width`; the pattern of six
     layers (latent, latent, retention, gated, two latent layers that read the second layer's cache) repeats."""
     H = width // 128
     latent = lambda kv_from=None: dict(type="latent_attention", mixer=dict(
-        heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=max(256, width // 4), scale=192 ** -0.5, mask=dict(size=1024),
+        heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=min(512, max(256, width // 4)), scale=192 ** -0.5, mask=dict(size=1024),
         rot=dict(base=500000.0, dims=64), **({} if kv_from is None else dict(kv_from=kv_from))))
     moe = dict(kind="moe", expert=dict(ff=width // 2, limit=7.0), router=dict(experts=32, top=4),
                shared=dict(ff=width, limit=7.0))

@@ -50,11 +50,74 @@ __global__ void short_conv_kernel(const float* __restrict__ h, const float* __re
     }
 }
 
+// The same for widths that are multiples of 4: a thread owns four neighbouring channels (16-byte loads).
+template <typename O>
+__global__ void short_conv4_kernel(const float* __restrict__ h, const float* __restrict__ w, float* __restrict__ state,
+                                   O* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ slots, const int* __restrict__ token_req, int D, int taps,
+                                   int max_slots, unsigned* err) {
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= D) return;
+    const int r = token_req[t];
+    const int a = q_start[r], n = q_len[r], i = t - a, slot = slots[r];
+    const int Hh = taps - 1;
+    const float* wc = w + (size_t)c * taps;                 // channel c + e: wc[e * taps + j]
+    if (i >= Hh) {
+        float4 acc = *reinterpret_cast<const float4*>(h + (size_t)t * D + c);
+        for (int j = 0; j < taps; ++j) {
+            const float4 x = *reinterpret_cast<const float4*>(h + (size_t)(t - Hh + j) * D + c);
+            acc.x = fmaf(wc[j], x.x, acc.x);
+            acc.y = fmaf(wc[taps + j], x.y, acc.y);
+            acc.z = fmaf(wc[2 * taps + j], x.z, acc.z);
+            acc.w = fmaf(wc[3 * taps + j], x.w, acc.w);
+        }
+        store4<O>(out + (size_t)t * D + c, acc);
+        return;
+    }
+    if (i != 0) return;
+    if (slot < 0 || slot >= max_slots) {
+        if (threadIdx.x == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
+        return;
+    }
+    float* st = state + (size_t)slot * Hh * D + c;
+    const int first = min(n, Hh);
+    for (int ii = 0; ii < first; ++ii) {
+        float4 acc = *reinterpret_cast<const float4*>(h + (size_t)(a + ii) * D + c);
+        for (int j = 0; j < taps; ++j) {
+            const int src = ii - Hh + j;
+            const float4 x = src >= 0 ? *reinterpret_cast<const float4*>(h + (size_t)(a + src) * D + c)
+                                      : *reinterpret_cast<const float4*>(st + (size_t)(src + Hh) * D);
+            acc.x = fmaf(wc[j], x.x, acc.x);
+            acc.y = fmaf(wc[taps + j], x.y, acc.y);
+            acc.z = fmaf(wc[2 * taps + j], x.z, acc.z);
+            acc.w = fmaf(wc[3 * taps + j], x.w, acc.w);
+        }
+        store4<O>(out + (size_t)(a + ii) * D + c, acc);
+    }
+    for (int k = 0; k < Hh; ++k) {
+        const int src = n - Hh + k;
+        *reinterpret_cast<float4*>(st + (size_t)k * D) =
+            src >= 0 ? *reinterpret_cast<const float4*>(h + (size_t)(a + src) * D + c)
+                     : *reinterpret_cast<const float4*>(st + (size_t)(n + k) * D);
+    }
+}
+
 extern "C" int aie_short_conv(const float* h, const float* w, float* state, void* out, int out_dtype, const int* q_start,
                               const int* q_len, const int* slots, const int* token_req, int T, int D, int taps,
                               int max_slots, unsigned* err, cudaStream_t st) {
     if (T <= 0) return 0;
     if (D <= 0 || taps < 1) return AIE_BAD_ARG;
+    if (D % 4 == 0 && !((size_t)h & 15) && !((size_t)state & 15) && !((size_t)out & 15)) {
+        const int threads = 64;
+        dim3 grid4(T, (D / 4 + threads - 1) / threads);
+        if (out_dtype == AIE_F32)
+            short_conv4_kernel<float><<<grid4, threads, 0, st>>>(h, w, state, (float*)out, q_start, q_len, slots, token_req, D, taps, max_slots, err);
+        else if (out_dtype == AIE_BF16)
+            short_conv4_kernel<bf16><<<grid4, threads, 0, st>>>(h, w, state, (bf16*)out, q_start, q_len, slots, token_req, D, taps, max_slots, err);
+        else
+            return AIE_BAD_ARG;
+        AIE_LAUNCH_CHECK();
+    }
     dim3 grid(T, (D + 255) / 256);
     if (grid.y > 65535) return AIE_UNSUPPORTED;
     if (out_dtype == AIE_F32)

@@ -588,9 +588,11 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     if T > TC_MAX_TOKENS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         # many tokens: the library's batched product, as for the other projections of a prompt step
         with region("gemm_library", _nb(x, w) + T * H * N * out.element_size(), 2.0 * T * H * N * K):
-            y = torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32) if out.dtype == torch.float32 \
-                else torch.bmm(x.transpose(0, 1), w.transpose(1, 2))
-            out[:, :, :N].copy_(y.transpose(0, 1))
+            dst = out[:, :, :N].transpose(0, 1)          # [H, T, N] view: the product is written in place
+            if out.dtype == torch.float32:
+                torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32, out=dst)
+            else:
+                torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=dst)
         return out
     return gemm_f32_ex(x, w, out, T, N, K, x.stride(0), out.stride(0), batch=H, a_bs=x.stride(1), w_bs=N * K,
                        c_bs=out.stride(1))

@@ -57,7 +57,11 @@ class TableMoE(FeedForward):
         if self.Fs:
             ws = [source.get(t[n]) for n in ("shared_gate", "shared_up", "shared_sg")]
             sdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
-            self.w_shared_in = torch.cat([w.to(sdt) for w in ws], dim=0).contiguous()      # [2 Fs + 1, hidden]
+            # [2 Fs + 1, hidden], with zero rows up to a multiple of 8: an odd row count would leave the rows of
+            # the product's output unaligned, which the library's fast kernels do not take
+            pad = (-(2 * self.Fs + 1)) % 8
+            ws.append(torch.zeros((pad, self.hidden), dtype=sdt, device=ws[0].device))
+            self.w_shared_in = torch.cat([w.to(sdt) for w in ws], dim=0).contiguous()
             self.w_shared_down = source.get(t["shared_down"])
 
     def weight_bytes(self):

@@ -95,10 +95,10 @@ def test_norm_with_a_weight_stored_around_zero(dtype, offset):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps", [1, 2, 3, 5])
-def test_short_convolution_carries_its_tail_across_portions_and_slots(dtype, taps):
+@pytest.mark.parametrize("taps,D", [(1, 72), (2, 72), (3, 70), (5, 72), (4, 1030)])
+def test_short_convolution_carries_its_tail_across_portions_and_slots(dtype, taps, D):
+    """Widths that are multiples of 4 take the kernel with four channels a thread, the others one channel."""
     from ai_engine_b200.parts import CausalShortConv, PartSpec
-    D = 72
     p = CausalShortConv(PartSpec("causal_short_conv", dict(size=D, taps=taps), dict(weight="w")), env(dtype, D))
     w = (0.5 * torch.randn(D, taps)).to(dtype)
     load(p, {"w": w}, dtype)

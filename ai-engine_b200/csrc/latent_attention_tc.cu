@@ -60,9 +60,13 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
     float* c_s = c_all + tq * LT_ROWS;
 
     // the 16 heads' queries, rounded to bfloat16 (rows past the last head are zero)
-    for (int e = ltid; e < LT_ROWS * dk; e += LT_THREADS) {
-        const int r = e / dk, c = e % dk;
-        q_s[r * SK + c] = __float2bfloat16_rn((active && h0 + r < H) ? q_full[((size_t)t * H + h0 + r) * dk + c] : 0.f);
+    for (int r = warp; r < LT_ROWS; r += 4) {                     // a warp converts whole rows, four elements a lane
+        const bool on = active && h0 + r < H;
+        const float* src = q_full + ((size_t)t * H + h0 + r) * dk;
+        for (int c = lane * 4; c < dk; c += 128) {
+            const float4 v = on ? *reinterpret_cast<const float4*>(src + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<uint2*>(q_s + r * SK + c) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+        }
     }
     if (ltid < LT_ROWS) {
         m_s[ltid] = -INFINITY;
@@ -76,35 +80,59 @@ latent_attention_tc_kernel(const float* __restrict__ q_full, const bf16* __restr
     for (int ch = c_begin; ch < c_end; ++ch) {
         const int k0 = ch * LT_KEYS;
         __syncthreads();                                          // the previous chunk's rows and probabilities are done with
-        for (int e = tid; e < LT_KEYS * pieces; e += THREADS) {
-            const int j = e / pieces, c = e % pieces, kp = k0 + j;
+        // a warp copies whole rows: one look-up of the page per row, the lanes take the row's 16-byte pieces
+        for (int j = tid >> 5; j < LT_KEYS; j += THREADS / 32) {
+            const int kp = k0 + j;
             bool ok = kp >= lo_first && kp <= pos_last;
             const bf16* src = pages;
             if (ok) {
                 const int pidx = kp / P;
                 const int page = pidx < bt_width ? block_table[(size_t)row * bt_width + pidx] : -1;
                 if (page < 0 || page >= num_pages) {
-                    if (c == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
+                    if (lane == 0) atomicOr(err, AIE_DEV_PAGE_OOB);
                     ok = false;
                 } else {
-                    src = pages + ((size_t)page * P + (kp - pidx * P)) * dk + c * 8;
+                    src = pages + ((size_t)page * P + (kp - pidx * P)) * dk;
                 }
             }
-            cp_async16(k_s + j * SK + c * 8, src, ok);
+            for (int c = lane; c < pieces; c += 32) cp_async16(k_s + j * SK + c * 8, ok ? src + c * 8 : pages, ok);
         }
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
 
         // S = Q K^T: warp w multiplies keys 16 w .. 16 w + 15
+        // two sets of accumulators take alternate k steps, so that a product does not wait for the one before it
+        // and the fragments of the next step are on their way while this step multiplies
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        for (int kk = 0; kk < dk; kk += 16) {
-            unsigned a[4], b0, b1, b2, b3;
-            ldsm_x4(a[0], a[1], a[2], a[3], q_s + (lane & 15) * SK + kk + (lane >> 4) * 8);
-            // rows = keys; matrices: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
-            ldsm_x4(b0, b1, b2, b3, k_s + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * SK + kk + ((lane >> 3) & 1) * 8);
+        float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const bf16* qa = q_s + (lane & 15) * SK + (lane >> 4) * 8;
+        // rows = keys; matrices: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
+        const bf16* kb = k_s + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * SK + ((lane >> 3) & 1) * 8;
+        int kk = 0;
+#pragma unroll 2
+        for (; kk + 32 <= dk; kk += 32) {
+            unsigned a[4], c[4], b0, b1, b2, b3, d0, d1, d2, d3;
+            ldsm_x4(a[0], a[1], a[2], a[3], qa + kk);
+            ldsm_x4(b0, b1, b2, b3, kb + kk);
+            ldsm_x4(c[0], c[1], c[2], c[3], qa + kk + 16);
+            ldsm_x4(d0, d1, d2, d3, kb + kk + 16);
             mma16816(s[0], a, b0, b1);
             mma16816(s[1], a, b2, b3);
+            mma16816(s2[0], c, d0, d1);
+            mma16816(s2[1], c, d2, d3);
+        }
+        if (kk < dk) {
+            unsigned a[4], b0, b1, b2, b3;
+            ldsm_x4(a[0], a[1], a[2], a[3], qa + kk);
+            ldsm_x4(b0, b1, b2, b3, kb + kk);
+            mma16816(s[0], a, b0, b1);
+            mma16816(s[1], a, b2, b3);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            s[0][e] += s2[0][e];
+            s[1][e] += s2[1][e];
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {

@@ -83,7 +83,7 @@ def make_dir(tmp_path, name, seed=0, gain=4.0):
             t = f.get_tensor(k)
             if k.endswith("mix.q") and gain != 1.0 and CONFIGS[name]["layers"][int(k[1:k.index(".")])]["type"] == "latent_attention":
                 t = (t.float() * gain).to(t.dtype)
-            tensors[k] = t.contiguous()
+            tensors[k] = t.clone().contiguous()          # a copy: the file is written again below
     save_file(tensors, path)
     return d
 

@@ -66,7 +66,7 @@ def folder(tmp_path, raw, seed):
 
     d = os.path.join(str(tmp_path), f"drawn{seed}")
     aie.write_random_model(aie.PifutarConfig.from_dict(raw), d, seed=seed, std=0.08, norm_std=0.1)
-    t = read_tensors(d)
+    t = {k: v.clone() for k, v in read_tensors(d).items()}       # copies: the file is written again below
     for k in list(t):          # attention scores that spread
         if k.endswith("mix.q") and raw["layers"][int(k[1:k.index(".")])]["type"] == "latent_attention":
             t[k] = (t[k].float() * 3.0).to(t[k].dtype)
@@ -74,7 +74,25 @@ def folder(tmp_path, raw, seed):
     return d, t
 
 
-@pytest.mark.parametrize("seed", range(10))
+def steady_rows(raw, t, ids, ref):
+    """Rows at which the model itself is well conditioned: a drawn model can make q . k of a head vanish at a
+    token (most often a sequence's first, where the state holds one key), and the normalised output of that head
+    then turns on the last bits of its inputs.  The oracle is run twice more with every matrix nudged by noise of
+    half a bfloat16 step; rows that move by more than 0.1 of the logits' spread are left out of the bfloat16
+    comparison (never more than half of them), all rows stay in the float32 one."""
+    g = torch.Generator().manual_seed(0)
+    moved = np.zeros(len(ids))
+    for _ in range(2):
+        t2 = {k: (v.double() * (1 + 2.0 ** -9 * torch.randn(v.shape, generator=g, dtype=torch.float64))
+                  if v.is_floating_point() and v.dim() == 2 else v) for k, v in t.items()}
+        out = pp.forward(raw, t2, ids, dtype=torch.float64).numpy()
+        moved = np.maximum(moved, np.abs(out - ref).max(1) / max(float(ref.std()), 1e-3))
+    keep = moved <= 0.1
+    assert keep.sum() >= len(ids) / 2, f"the drawn model is ill-conditioned at {int((~keep).sum())} of {len(ids)} rows"
+    return keep
+
+
+@pytest.mark.parametrize("seed", range(24))
 def test_a_drawn_configuration(tmp_path, seed):
     from ai_engine_b200.engine.replay import Replayer
 
@@ -84,9 +102,12 @@ def test_a_drawn_configuration(tmp_path, seed):
     for dtype in ("float32", "bfloat16"):
         ref_a = pp.forward(raw, t, a, dtype=oracle_dtype(dtype)).double().numpy()
         ref_b = pp.forward(raw, t, b, dtype=oracle_dtype(dtype)).double().numpy()
+        ka = kb = slice(None)
+        if dtype == "bfloat16":
+            ka, kb = steady_rows(raw, t, a, ref_a), steady_rows(raw, t, b, ref_b)
         rep = Replayer(d, dtype, max_tokens=192, block_size=int([8, 16, 32][seed % 3]))
         whole = rep.run_step([dict(id="w", tokens=a, want=list(range(70)))], end=["w"]).numpy()
-        close(whole, ref_a, dtype, f"drawn {seed} whole {raw['layers']}")
+        close(whole[ka], ref_a[ka], dtype, f"drawn {seed} whole {raw['layers']}")
         # in portions, with a second request beside it that starts later and ends earlier
         got_a, got_b, fa, fb = [], [], 0, 0
         for k, n in enumerate([9, 2, 17, 1, 1, 30, 3, 7]):
@@ -98,5 +119,5 @@ def test_a_drawn_configuration(tmp_path, seed):
             if len(entries) == 2:
                 got_b.append(out[:m]); out = out[m:]; fb += m
             got_a.append(out); fa += n
-        close(np.concatenate(got_a), ref_a, dtype, f"drawn {seed} in portions")
-        close(np.concatenate(got_b), ref_b, dtype, f"drawn {seed} the request beside it")
+        close(np.concatenate(got_a)[ka], ref_a[ka], dtype, f"drawn {seed} in portions")
+        close(np.concatenate(got_b)[kb], ref_b[kb], dtype, f"drawn {seed} the request beside it")

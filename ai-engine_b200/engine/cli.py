@@ -95,8 +95,9 @@ def check_only(options: dict) -> None:
     arch, cfg = load_config(opts.weights_path)
     if not opts.random_weights:
         folder = ModelFolder(opts.weights_path)
-        check_and_resolve(tensor_specs_of(arch.build_spec(cfg)),
-                          {n: folder.info(n) for n in folder.names()}, where=opts.weights_path)
+        spec = arch.build_spec(cfg)
+        check_and_resolve(tensor_specs_of(spec), {n: folder.info(n) for n in folder.names()},
+                          where=opts.weights_path, ignored=spec.ignored_tensors)
         folder.close()
 
 

@@ -206,3 +206,25 @@ def test_the_trace_program_on_a_pifutar_folder(tmp_path):
     got2 = np.fromfile(os.path.join(out_dir, "2.f32"), dtype="<f4").reshape(1, -1)
     close(got0, ref[[0, 20]], "float32", "trace step 0")
     close(got2, ref[[29]], "float32", "trace step 2")
+
+
+def test_the_command_line_on_a_pifutar_folder(tmp_path):
+    d = make_dir(tmp_path, "Z")
+    exe = [sys.executable, os.path.join(ROOT, "bin", "ai-engine")]
+    assert subprocess.run(exe + ["--model", d, "--check"], capture_output=True, text=True).stdout.strip() == "ok"
+    p = subprocess.run(exe + ["--model", d, "--dtype", "fp32", "--prompt-ids", "5,17,3,200", "--prompt-ids", "9",
+                              "--max-tokens", "5", "--ignore-eos", "--profile"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-1500:]
+    lines = [[int(t) for t in l.split(",")] for l in p.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(l) == 5 for l in lines)
+    for cls in ("latent_attention", "linear_recurrence", "short_conv", "depth_average", "expert_combine"):
+        assert cls in p.stderr, cls
+    raw, t = CONFIGS["Z"], read_tensors(d)
+    st = pp.State()
+    logits = pp.forward(raw, t, [5, 17, 3, 200], st)[-1]
+    for k in range(5):
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) < 1e-3 * float(logits.std()):
+            break
+        assert lines[0][k] == int(torch.argmax(logits))
+        logits = pp.forward(raw, t, [lines[0][k]], st)[-1]

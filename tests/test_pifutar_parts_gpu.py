@@ -229,6 +229,13 @@ LATENT_CASES = [
     dict(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40, scale=0.2, rot=dict(base=10000.0, dims=8), mask=dict(size=11)),
     dict(heads=20, dim=16, rot_dim=16, vdim=8, kv_rank=128, scale=0.18, rot=dict(base=500000.0, dims=16), mask=dict(size=70)),
     dict(heads=4, dim=32, rot_dim=32, vdim=16, kv_rank=64, scale=0.125, rot=dict(base=100.0, dims=16)),
+    # every width of the tensor-core kernel's column split: latents of 192, 256, 320, 384, 448 and 512
+    dict(heads=3, dim=16, rot_dim=16, vdim=8, kv_rank=192, scale=0.2, rot=dict(base=10000.0, dims=16), mask=dict(size=33)),
+    dict(heads=17, dim=8, rot_dim=32, vdim=8, kv_rank=256, scale=0.2, rot=dict(base=10000.0, dims=32), mask=dict(size=64)),
+    dict(heads=2, dim=24, rot_dim=16, vdim=8, kv_rank=320, scale=0.15, rot=dict(base=10000.0, dims=16)),
+    dict(heads=5, dim=16, rot_dim=16, vdim=8, kv_rank=384, scale=0.2, rot=dict(base=10000.0, dims=16), mask=dict(size=65)),
+    dict(heads=1, dim=16, rot_dim=16, vdim=8, kv_rank=448, scale=0.2, rot=dict(base=10000.0, dims=16), mask=dict(size=129)),
+    dict(heads=16, dim=32, rot_dim=64, vdim=16, kv_rank=512, scale=0.1, rot=dict(base=500000.0, dims=64), mask=dict(size=100)),
 ]
 
 

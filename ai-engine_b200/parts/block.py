@@ -7,6 +7,10 @@ float32, stores the sum and normalises it in one pass over the row.
 """
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
 from .base import Block
 
 
@@ -55,7 +59,6 @@ class DepthAveragedBlock(Block):
         self.coef = None
 
     def tensor_specs(self):
-        from ..weights.loader import TensorSpec
         name = self.spec.tensors.get("coef")
         n = self.depth + 2
         return [TensorSpec(name, (n,), mean=1.0 / n, std=0.1 / n)] if name else []
@@ -68,14 +71,10 @@ class DepthAveragedBlock(Block):
     def _filtered(self, role, h, ctx, caches):
         f = self.p.get(role)
         if f is None:
-            from ..kernels import ops
             return ops.cast(h, self.env.dtype)
         return f.forward(h, ctx, caches[role])
 
     def forward(self, x, pending, ctx, caches):
-        import torch
-
-        from ..kernels import ops
         h = self.p["mixer_norm"].forward(x, pending)
         if self.coef is not None:
             if self.depth == 0:

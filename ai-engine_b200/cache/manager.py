@@ -98,18 +98,19 @@ class PagedCache:
                 r = g.request
                 g.pool = torch.full((len(g.entries), r.planes, g.num_pages, r.kv_heads, g.page_size, r.head_dim),
                                     float("nan"), dtype=dtype, device=self.device)
+            make = lambda st: torch.zeros((self.max_seqs,) + tuple(st.shape), dtype=st.dtype, device=self.device)
             for n in self.requests:
-                if n.state is not None:
-                    self.state[n.run, n.role] = torch.zeros((self.max_seqs,) + tuple(n.state.shape),
-                                                            dtype=n.state.dtype, device=self.device)
+                if isinstance(n.state, dict):          # a part that keeps several tensors
+                    self.state[n.run, n.role] = {name: make(st) for name, st in n.state.items()}
+                elif n.state is not None:
+                    self.state[n.run, n.role] = make(n.state)
 
     # -- requests ---------------------------------------------------------------
     def admit(self) -> int:
         """A slot for a new request (-1: none free); its state starts at zero."""
         slot = self.book.admit()
         if slot >= 0:
-            for t in self.state.values():
-                t[slot].zero_()
+            self.reset_state(slot)
         return slot
 
     def ensure(self, slot: int, n_tokens: int) -> bool:
@@ -121,8 +122,13 @@ class PagedCache:
     def finish(self, slot: int) -> None:
         self.book.finish(slot)
 
-    def reset_state(self, slot: int) -> None:
+    def state_tensors(self):
+        """Every state tensor, whichever part holds it."""
         for t in self.state.values():
+            yield from (t.values() if isinstance(t, dict) else (t,))
+
+    def reset_state(self, slot: int) -> None:
+        for t in self.state_tensors():
             t[slot].zero_()
 
     # -- the step's view ----------------------------------------------------------
@@ -143,8 +149,26 @@ class PagedCache:
         return lc
 
     def layer_cache(self, run_index: int, ctx) -> Dict[str, LayerCache]:
-        """role -> LayerCache for the parts of run-order entry `run_index` that asked for pages or state."""
-        return {role: self.part_cache(run_index, role, ctx) for role in self.roles.get(run_index, ())}
+        """role -> LayerCache for the parts of run-order entry `run_index` that asked for pages or state.  A part
+        inside a composite part (role `<role>.<name>`) is found under its composite's `children[name]`."""
+        out: Dict[str, LayerCache] = {}
+        for role in self.roles.get(run_index, ()):
+            lc = self.part_cache(run_index, role, ctx)
+            names = role.split(".")
+            if len(names) == 1:
+                if role in out:                      # made earlier as the holder of a child's cache
+                    lc.children = out[role].children
+                out[role] = lc
+                continue
+            at = out.setdefault(names[0], LayerCache())
+            for name in names[1:-1]:
+                at.children = at.children or {}
+                at = at.children.setdefault(name, LayerCache())
+            at.children = at.children or {}
+            if names[-1] in at.children:
+                lc.children = at.children[names[-1]].children
+            at.children[names[-1]] = lc
+        return out
 
     # -- accounting -----------------------------------------------------------------
     def kv_bytes_per_token(self) -> int:

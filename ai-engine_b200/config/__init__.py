@@ -9,3 +9,6 @@ __all__ = ["ConfigError", "read_json", "LlamaConfig", "RopeScaling", "Architectu
 from .pifutar import PifutarConfig  # noqa: E402
 
 __all__.append("PifutarConfig")
+from .zupitar import ZupitarConfig  # noqa: E402
+
+__all__.append("ZupitarConfig")

@@ -275,8 +275,15 @@ extern "C" int aie_add_rmsnorm(float* x, const void* delta, int delta_dtype, con
 // in float32.  block == 0: gu[t] = [gate (F) | up (F)].  block > 0: gu[t] is in groups of
 // 2 * block columns, `block` gate columns followed by their `block` up columns.
 // ---------------------------------------------------------------------------
+// the activation of a gated unit: 0 silu, 1 relu, 2 gelu (tanh form)
+__device__ __forceinline__ float glu_act(float g, int act) {
+    if (act == 1) return fmaxf(g, 0.f);
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g * (1.0f / (1.0f + expf(-g)));
+}
+
 template <typename A>
-__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int F, int block, size_t total) {
+__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int F, int block, size_t total, int act) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -287,15 +294,14 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ a, int
         const size_t uc = block ? gc + block : F + f;
         const float g = to_f32<A>(gu[t * 2 * F + gc]);
         const float u = to_f32<A>(gu[t * 2 * F + uc]);
-        const float s = g * (1.0f / (1.0f + expf(-g)));
-        a[i] = from_f32<A>(s * u);
+        a[i] = from_f32<A>(glu_act(g, act) * u);
     }
 }
 
 // Eight outputs per thread with 16-byte accesses (bfloat16) when F and the group size are
 // multiples of 8.
 __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ a, int F, int block,
-                                     size_t total8) {
+                                     size_t total8, int act) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -317,6 +323,10 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
             // sigmoid by ex2.approx and rcp.approx (relative error about 1e-6, far below the bf16 rounding of
             // the result): with expf and a division the kernel was bound by instruction issue, not by memory
             const float g = __bfloat162float(ge[j]), u = __bfloat162float(ue[j]);
+            if (act) {
+                oe[j] = __float2bfloat16_rn(glu_act(g, act) * u);
+                continue;
+            }
             float e, r;
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
             asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
@@ -326,8 +336,8 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, int block, cudaStream_t stream) {
-    if (block < 0 || (block && F % block)) return AIE_BAD_ARG;
+extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, int block, int act, cudaStream_t stream) {
+    if (block < 0 || (block && F % block) || act < 0 || act > 2) return AIE_BAD_ARG;
     if (T <= 0) return 0;
     const size_t total = (size_t)T * F;
     int blocks = (int)((total + 255) / 256);
@@ -336,13 +346,13 @@ extern "C" int aie_silu_mul(const void* gu, void* a, int dtype, int T, int F, in
         const size_t total8 = total / 8;
         int b8 = (int)((total8 + 255) / 256);
         if (b8 > aie_sm_count() * 16) b8 = aie_sm_count() * 16;
-        launch_pdl(silu_mul_vec8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total8);
+        launch_pdl(silu_mul_vec8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total8, act);
         AIE_LAUNCH_CHECK();
     }
     if (dtype == AIE_F32)
-        launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)a, F, block, total);
+        launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)a, F, block, total, act);
     else if (dtype == AIE_BF16)
-        launch_pdl(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total);
+        launch_pdl(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)a, F, block, total, act);
     else
         return AIE_BAD_ARG;
     AIE_LAUNCH_CHECK();
@@ -369,5 +379,49 @@ extern "C" int aie_cast(const void* in, int in_dtype, void* out, int out_dtype, 
         cast_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
     else
         return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// x <- cap * tanh(x / cap), float32, in place (logits kept within +-cap)
+// ---------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+extern "C" int aie_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return AIE_BAD_ARG;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    softcap_kernel<<<blocks, 256, 0, stream>>>(x, (size_t)n, cap, 1.0f / cap);
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// out = sa * a + sb * b, float32 (two branches that read the same input, each with its weight); a and b may be
+// [parts, n]: the unjoined parts of a split product, added in order before the scaling
+// ---------------------------------------------------------------------------
+__global__ void scaled_sum_kernel(const float* __restrict__ a, int pa, float sa, const float* __restrict__ b, int pb,
+                                  float sb, float* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        float x = a[i], y = b[i];
+        for (int p = 1; p < pa; ++p) x += a[(size_t)p * n + i];
+        for (int p = 1; p < pb; ++p) y += b[(size_t)p * n + i];
+        out[i] = fmaf(sb, y, sa * x);
+    }
+}
+
+extern "C" int aie_scaled_sum(const float* a, int pa, float sa, const float* b, int pb, float sb, float* out,
+                              long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (pa < 1 || pb < 1) return AIE_BAD_ARG;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > aie_sm_count() * 16) blocks = aie_sm_count() * 16;
+    scaled_sum_kernel<<<blocks, 256, 0, stream>>>(a, pa, sa, b, pb, sb, out, (size_t)n);
     AIE_LAUNCH_CHECK();
 }

@@ -1,8 +1,11 @@
 // Linear attention with a decaying matrix state, per request and head:
 //     S_t = diag(a_t) S_(t-1) + k_t v_t^T        (S: [d, dv], a_t per key channel)
 //     o_t = S_t^T q_t
-// a_t is a constant per head (retention) or a per-token, per-channel value (gated linear attention).  The
-// state is float32, lives in the request's slot and is carried from step to step.
+// a_t is a constant per head (retention), a per-token, per-channel value (gated linear attention), or one number
+// per token and head made here from a step size (a selective state space: dt = softplus(raw + bias),
+// a = exp(-exp(a_log) dt), the value scaled by dt, queries and keys shared by `hpg` neighbouring heads, and
+// skip[h] v added to the output).  The state is float32, lives in the request's slot and is carried from step
+// to step.
 //
 // The columns of S never mix: column j needs only v_t[j].  A warp owns 32 / lanes columns of one (request,
 // head); `lanes` threads share a column, each with RPT consecutive rows of S in registers, and a token costs
@@ -23,7 +26,9 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          const float* __restrict__ decay_tok, int ld_decay, const float* __restrict__ decay_head,
                          float q_scale, float k_scale, float* __restrict__ state, float* __restrict__ out,
                          const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ slots,
-                         int H, int d, int dv, int lanes, int groups, int TT, int max_slots, int vec, int vec4, unsigned* err) {
+                         int H, int d, int dv, int lanes, int groups, int TT, int max_slots, int vec, int vec4, unsigned* err,
+                         int hpg, const float* __restrict__ dt_raw, int ld_dt, const float* __restrict__ dt_bias,
+                         const float* __restrict__ a_log, const float* __restrict__ skip) {
     extern __shared__ __align__(16) float lr_sm[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bg = blockIdx.x % groups, h = (blockIdx.x / groups) % H, r = blockIdx.x / (groups * H);
@@ -37,6 +42,9 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     float* k_s = q_s + TT * d;
     float* a_s = k_s + TT * d;                                    // only with per-token decays
     float* v_s = decay_tok ? a_s + TT * d : a_s;                  // [TT][CB]
+    float* sc_s = v_s + TT * (LR_WARPS * (32 / lanes));           // [TT][2]: decay and step size (only with dt_raw)
+    const int hq = h / hpg;                                       // the head whose queries and keys this one reads
+    const float rate = dt_raw ? expf(a_log[h]) : 0.f, dtb = dt_raw ? dt_bias[h] : 0.f;
     const int g = lane % lanes, cb = warp * cols + lane / lanes, col = bg * CB + cb;
     const int row0 = g * RPT;
     const bool col_ok = col < dv;
@@ -50,8 +58,18 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
         const int nt = min(TT, n - t0);
         __syncthreads();                                          // the previous tokens are done with
         for (int tok = warp; tok < nt; tok += LR_WARPS) {          // a warp stages a token's rows
-            const size_t at = (size_t)(a + t0 + tok) * ld + h * d;
+            const size_t at = (size_t)(a + t0 + tok) * ld + hq * d;
             const size_t at_a = (size_t)(a + t0 + tok) * ld_decay + h * d;
+            float vs = k_scale;
+            if (dt_raw) {                                          // float32: softplus, then the decay of this token
+                const float x = dt_raw[(size_t)(a + t0 + tok) * ld_dt + h] + dtb;
+                const float dtv = x > 20.f ? x : log1pf(expf(x));
+                if (lane == 0) {
+                    sc_s[tok * 2] = expf(-rate * dtv);
+                    sc_s[tok * 2 + 1] = dtv;
+                }
+                vs *= dtv;
+            }
             if (vec4) {
                 for (int c = lane * 4; c < d; c += 128) {
                     *reinterpret_cast<float4*>(q_s + tok * d + c) = *reinterpret_cast<const float4*>(q + at + c);
@@ -66,7 +84,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                 }
             }
             for (int c = lane; c < CB; c += 32)
-                v_s[tok * CB + c] = bg * CB + c < dv ? v[(size_t)(a + t0 + tok) * ld + h * dv + bg * CB + c] * k_scale : 0.f;
+                v_s[tok * CB + c] = bg * CB + c < dv ? v[(size_t)(a + t0 + tok) * ld + h * dv + bg * CB + c] * vs : 0.f;
         }
         __syncthreads();
         // the staged tokens' updates first, then their reductions over the column's lanes side by side (sixteen
@@ -80,6 +98,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
             const float* kr = k_s + tok * d + row0;
             const float* ar = decay_tok ? a_s + tok * d + row0 : nullptr;
             const float vv = v_s[tok * CB + cb];
+            const float dh_t = dt_raw ? sc_s[tok * 2] : dh;
             float o = 0.f, o2 = 0.f;                               // two chains of additions
             if (vec) {
 #pragma unroll
@@ -87,7 +106,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                     if (row0 + i < d) {
                         const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
                         const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
-                        float4 a4 = make_float4(dh, dh, dh, dh);
+                        float4 a4 = make_float4(dh_t, dh_t, dh_t, dh_t);
                         if (ar) a4 = *reinterpret_cast<const float4*>(ar + i);
                         S[i] = fmaf(a4.x, S[i], k4.x * vv);
                         S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
@@ -103,7 +122,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
 #pragma unroll
                 for (int i = 0; i < RPT; ++i) {
                     if (row0 + i < d) {
-                        const float al = ar ? ar[i] : dh;
+                        const float al = ar ? ar[i] : dh_t;
                         S[i] = fmaf(al, S[i], kr[i] * vv);
                         o = fmaf(S[i], qr[i], o);
                     }
@@ -118,7 +137,11 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
         if (g == 0 && col_ok) {
 #pragma unroll
             for (int tok = 0; tok < LR_TOKENS; ++tok)
-                if (tok < nt) out[((size_t)(a + t0 + tok) * H + h) * dv + col] = oacc[tok] * q_scale;
+                if (tok < nt) {
+                    float o = oacc[tok] * q_scale;
+                    if (skip) o = fmaf(skip[h], v[(size_t)(a + t0 + tok) * ld + h * dv + col], o);
+                    out[((size_t)(a + t0 + tok) * H + h) * dv + col] = o;
+                }
         }
     }
     if (col_ok) {
@@ -131,12 +154,17 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
 // q, k [T, .] with head h's d channels at column h d of rows `ld` floats apart; v likewise with dv columns a
 // head; decay_tok [T, .] rows `ld_decay` apart (or null: decay_head [H] constants).  The key is scaled by
 // k_scale, the output by q_scale (both 1 or d^-1/2).  state [max_slots, H, d, dv]; out [T, H, dv].
+// dt_raw [T, .] (rows ld_dt apart, head h at column h) with dt_bias, a_log [H]: the decay comes from the step size
+// as the header says; hpg: heads that share one head of q and k (1: each its own); skip [H] or null.
 extern "C" int aie_linear_recurrence(const float* q, const float* k, const float* v, int ld, const float* decay_tok,
                                      int ld_decay, const float* decay_head, float q_scale, float k_scale, float* state,
                                      float* out, const int* q_start, const int* q_len, const int* slots, int T, int R,
-                                     int H, int d, int dv, int max_slots, unsigned* err, cudaStream_t st) {
+                                     int H, int d, int dv, int max_slots, unsigned* err, int hpg, const float* dt_raw,
+                                     int ld_dt, const float* dt_bias, const float* a_log, const float* skip,
+                                     cudaStream_t st) {
     if (R <= 0) return 0;
-    if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head)) return AIE_BAD_ARG;
+    if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head && !dt_raw)) return AIE_BAD_ARG;
+    if (hpg < 1 || H % hpg || (dt_raw && (!dt_bias || !a_log || decay_tok))) return AIE_BAD_ARG;
     if (d > 1024) return AIE_UNSUPPORTED;
     // A step of single tokens is bound by reading and writing the states: many rows a thread, so that a warp's
     // accesses to a row of the state are wide.  A step of prompt portions is bound by the chain of dependent
@@ -150,7 +178,7 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
     if (blocks > 0x7fffffffLL) return AIE_UNSUPPORTED;
     int TT = 3072 / d;      // at most 36 KB of staged queries, keys and decays
     TT = TT < 1 ? 1 : (TT > LR_TOKENS ? LR_TOKENS : TT);
-    const size_t smem = ((size_t)TT * d * (decay_tok ? 3 : 2) + (size_t)TT * CB) * sizeof(float);
+    const size_t smem = ((size_t)TT * d * (decay_tok ? 3 : 2) + (size_t)TT * CB + 2 * TT) * sizeof(float);
     // rows of the staged tokens are read as float4: the head's width and every thread's first row are multiples of 4
     const int vec = d % 4 == 0 ? 1 : 0;
     // ... and the rows in memory too when the row strides and base addresses allow 16-byte loads
@@ -160,7 +188,8 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
     linear_recurrence_kernel<N><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
                                                                      q_scale, k_scale, state, out, q_start, q_len,  \
                                                                      slots, H, d, dv, lanes, groups, TT, max_slots, \
-                                                                     vec, vec4, err)
+                                                                     vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
+                                                                     a_log, skip)
     if (rpt == 4) GO(4);
     else if (rpt == 8) GO(8);
     else if (rpt == 16) GO(16);

@@ -294,7 +294,9 @@ extern "C" int aie_gated_decay(const float* z, const float* bias, float* out, lo
 }
 
 // ---------------------------------------------------------------------------
-// Experts chosen by a table of the token's id: pair p = (token t, choice s) goes to expert table[id[t], s].
+// Experts chosen by a table of the token's id: pair p = (token t, choice s) goes to expert table[id[t], s]
+// (ids null: the table has a row per token of the step, as a router leaves it).  Experts E .. E + ident - 1 are
+// accepted but get no row: they stand for experts without weights, and their pairs are marked with -2.
 // One block groups the pairs by expert into tiles of `tile` rows (each expert's rows padded up to whole tiles):
 //   row_token[row]  = token of the row, -1 for padding         [n_tiles * tile]
 //   pair_row[p]     = row of pair p (-1: bad token id or expert)  [T * top]
@@ -303,7 +305,7 @@ extern "C" int aie_gated_decay(const float* z, const float* bias, float* out, lo
 // of the grouped products is computed for itself.
 // ---------------------------------------------------------------------------
 __global__ void expert_plan_kernel(const int* __restrict__ ids, const int* __restrict__ table, int T, int V, int top,
-                                   int E, int tile, int n_tiles, int* __restrict__ row_token, int* __restrict__ pair_row,
+                                   int E, int ident, int tile, int n_tiles, int* __restrict__ row_token, int* __restrict__ pair_row,
                                    int* __restrict__ tile_expert, unsigned* err) {
     extern __shared__ int sh[];
     int* count = sh;            // [E]
@@ -315,9 +317,10 @@ __global__ void expert_plan_kernel(const int* __restrict__ ids, const int* __res
     for (int i = tid; i < n_tiles; i += blockDim.x) tile_expert[i] = -1;
     __syncthreads();
     for (int p = tid; p < P; p += blockDim.x) {
-        const int id = ids[p / top];
+        const int id = ids ? ids[p / top] : p / top;
         int e = -1;
         if (id >= 0 && id < V) e = table[(size_t)id * top + p % top];
+        if (e >= E && e < E + ident) continue;
         if (e < 0 || e >= E) {
             atomicOr(err, AIE_DEV_TOKEN_OOB);
             continue;
@@ -336,11 +339,11 @@ __global__ void expert_plan_kernel(const int* __restrict__ ids, const int* __res
     }
     __syncthreads();
     for (int p = tid; p < P; p += blockDim.x) {
-        const int id = ids[p / top];
+        const int id = ids ? ids[p / top] : p / top;
         int e = -1;
         if (id >= 0 && id < V) e = table[(size_t)id * top + p % top];
         if (e < 0 || e >= E) {
-            pair_row[p] = -1;
+            pair_row[p] = (e >= E && e < E + ident) ? -2 : -1;
             continue;
         }
         const int row = start[e] + atomicAdd(&cursor[e], 1);
@@ -349,12 +352,12 @@ __global__ void expert_plan_kernel(const int* __restrict__ ids, const int* __res
     }
 }
 
-extern "C" int aie_expert_plan(const int* ids, const int* table, int T, int V, int top, int E, int tile, int n_tiles,
+extern "C" int aie_expert_plan(const int* ids, const int* table, int T, int V, int top, int E, int ident, int tile, int n_tiles,
                                int* row_token, int* pair_row, int* tile_expert, unsigned* err, cudaStream_t st) {
     if (T <= 0) return 0;
     if (top <= 0 || E <= 0 || tile <= 0 || (long long)n_tiles * tile < (long long)T * top) return AIE_BAD_ARG;
     if ((size_t)3 * E * sizeof(int) > 40000) return AIE_UNSUPPORTED;
-    expert_plan_kernel<<<1, 1024, 3 * E * sizeof(int), st>>>(ids, table, T, V, top, E, tile, n_tiles, row_token, pair_row,
+    expert_plan_kernel<<<1, 1024, 3 * E * sizeof(int), st>>>(ids, table, T, V, top, E, ident, tile, n_tiles, row_token, pair_row,
                                                               tile_expert, err);
     AIE_LAUNCH_CHECK();
 }
@@ -402,5 +405,220 @@ extern "C" int aie_gather_rows(const void* src, const int* rows, void* out, int 
         gather_rows_kernel<bf16><<<n, 256, 0, st>>>((const bf16*)src, rows, (bf16*)out, D);
     else
         return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// A causal convolution over time on a slice of a wider projection, per channel:
+//   y[t, c] = (residual ? u[t, c] : 0) + bias[c] + sum_j w[c, j] * u[t - (taps-1) + j, c],   then act (0: none, 1: silu)
+// u rows are ld_in floats apart, out rows ld_out elements.  Channels [dup_from, dup_from + dup_n) are written a
+// second time dup_n columns further on (keys that are also values).  The inputs of the taps-1 tokens before a
+// portion are the request's tail `state[slot]` [taps-1, C]; as in short_conv only the block of a request's first
+// token of the step reads and replaces it.
+// ---------------------------------------------------------------------------
+template <typename O>
+__global__ void causal_conv_kernel(const float* __restrict__ u, int ld_in, const float* __restrict__ w,
+                                   const float* __restrict__ bias, float* __restrict__ state, O* __restrict__ out,
+                                   int ld_out, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ slots, const int* __restrict__ token_req, int C, int taps,
+                                   int residual, int act, int dup_from, int dup_n, int max_slots, unsigned* err) {
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int r = token_req[t];
+    const int a = q_start[r], n = q_len[r], i = t - a, slot = slots[r];
+    const int Hh = taps - 1;
+    const float* wc = w + (size_t)c * taps;
+    const float b = bias ? bias[c] : 0.f;
+    const bool dup = c >= dup_from && c < dup_from + dup_n;
+    if (i >= Hh) {
+        float acc = residual ? u[(size_t)t * ld_in + c] + b : b;
+        for (int j = 0; j < taps; ++j) acc = fmaf(wc[j], u[(size_t)(t - Hh + j) * ld_in + c], acc);
+        if (act == 1) acc = acc / (1.0f + expf(-acc));
+        out[(size_t)t * ld_out + c] = from_f32<O>(acc);
+        if (dup) out[(size_t)t * ld_out + c + dup_n] = from_f32<O>(acc);
+        return;
+    }
+    if (i != 0) return;
+    if (slot < 0 || slot >= max_slots) {
+        if (threadIdx.x == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
+        return;
+    }
+    float* st = state + (size_t)slot * Hh * C + c;          // st[k * C]: input at local index k - Hh
+    const int first = min(n, Hh);
+    for (int ii = 0; ii < first; ++ii) {
+        float acc = residual ? u[(size_t)(a + ii) * ld_in + c] + b : b;
+        for (int j = 0; j < taps; ++j) {
+            const int src = ii - Hh + j;
+            const float x = src >= 0 ? u[(size_t)(a + src) * ld_in + c] : st[(size_t)(src + Hh) * C];
+            acc = fmaf(wc[j], x, acc);
+        }
+        if (act == 1) acc = acc / (1.0f + expf(-acc));
+        out[(size_t)(a + ii) * ld_out + c] = from_f32<O>(acc);
+        if (dup) out[(size_t)(a + ii) * ld_out + c + dup_n] = from_f32<O>(acc);
+    }
+    for (int k = 0; k < Hh; ++k) {                          // ascending: entry n + k > k is still the old one
+        const int src = n - Hh + k;
+        st[(size_t)k * C] = src >= 0 ? u[(size_t)(a + src) * ld_in + c] : st[(size_t)(n + k) * C];
+    }
+}
+
+extern "C" int aie_causal_conv(const float* u, int ld_in, const float* w, const float* bias, float* state, void* out,
+                               int out_dtype, int ld_out, const int* q_start, const int* q_len, const int* slots,
+                               const int* token_req, int T, int C, int taps, int residual, int act, int dup_from,
+                               int dup_n, int max_slots, unsigned* err, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (C <= 0 || taps < 1 || act < 0 || act > 1 || dup_n < 0 || (dup_n && (dup_from < 0 || dup_from + dup_n != C)))
+        return AIE_BAD_ARG;
+    const int threads = C >= 256 ? 256 : 128;
+    dim3 grid(T, (C + threads - 1) / threads);
+    if (grid.y > 65535) return AIE_UNSUPPORTED;
+    if (out_dtype == AIE_F32)
+        causal_conv_kernel<float><<<grid, threads, 0, st>>>(u, ld_in, w, bias, state, (float*)out, ld_out, q_start, q_len, slots, token_req, C, taps, residual, act, dup_from, dup_n, max_slots, err);
+    else if (out_dtype == AIE_BF16)
+        causal_conv_kernel<bf16><<<grid, threads, 0, st>>>(u, ld_in, w, bias, state, (bf16*)out, ld_out, q_start, q_len, slots, token_req, C, taps, residual, act, dup_from, dup_n, max_slots, err);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// Gate, then norm in equal parts of the width: g = y * silu(z); out = g / sqrt(mean_part(g^2) + eps) * w.
+// y [T, W] float32; z rows of ldz floats (a slice of a wider projection); w [W]; `parts` equal parts of W,
+// each divided by its own root mean square.  One block per (token, part).
+// ---------------------------------------------------------------------------
+template <typename O>
+__global__ void gate_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz,
+                                       const float* __restrict__ w, O* __restrict__ out, int W, int parts, float eps) {
+    __shared__ float red[32];
+    const int t = blockIdx.x / parts, p = blockIdx.x % parts, n = W / parts;
+    const float* yr = y + (size_t)t * W + (size_t)p * n;
+    const float* zr = z + (size_t)t * ldz + (size_t)p * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float zv = zr[i], g = yr[i] * (zv / (1.0f + expf(-zv)));
+        ss = fmaf(g, g, ss);
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float zv = zr[i], g = yr[i] * (zv / (1.0f + expf(-zv)));
+        out[(size_t)t * W + (size_t)p * n + i] = from_f32<O>(g * r * w[(size_t)p * n + i]);
+    }
+}
+
+extern "C" int aie_gate_group_norm(const float* y, const float* z, int ldz, const float* w, void* out, int out_dtype,
+                                   int T, int W, int parts, float eps, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (W <= 0 || parts <= 0 || W % parts) return AIE_BAD_ARG;
+    const int n = W / parts, threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+    const long long blocks = (long long)T * parts;
+    if (blocks > 0x7fffffffLL) return AIE_UNSUPPORTED;
+    if (out_dtype == AIE_F32)
+        gate_group_norm_kernel<float><<<(unsigned)blocks, threads, 0, st>>>(y, z, ldz, w, (float*)out, W, parts, eps);
+    else if (out_dtype == AIE_BF16)
+        gate_group_norm_kernel<bf16><<<(unsigned)blocks, threads, 0, st>>>(y, z, ldz, w, (bf16*)out, W, parts, eps);
+    else
+        return AIE_BAD_ARG;
+    AIE_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// A router's choice, per token, float32: s = softmax(z) over the E outputs; the choice is made on s + correction;
+// the outputs form `groups` equal groups of neighbours, a group counts as its best member, and only members of the
+// `keep` best groups can be chosen (the others count as minus infinity); the `top` largest are taken, and their
+// weights are their s.  z [T, E] is replaced by s; scratch [T, E]; ids, weights [T, top].  One thread per token.
+// ---------------------------------------------------------------------------
+__global__ void route_topk_kernel(float* __restrict__ z, float* __restrict__ scratch, const float* __restrict__ corr,
+                                  int T, int E, int groups, int keep, int top, int* __restrict__ ids,
+                                  float* __restrict__ weights) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    float* s = z + (size_t)t * E;
+    float* c = scratch + (size_t)t * E;
+    float m = -INFINITY;
+    for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) {
+        const float v = expf(s[e] - m);
+        s[e] = v;
+        sum += v;
+    }
+    for (int e = 0; e < E; ++e) {
+        s[e] = s[e] / sum;
+        c[e] = s[e] + (corr ? corr[e] : 0.f);
+    }
+    const int per = E / groups;
+    if (keep < groups) {
+        unsigned long long kept = 0ull;                     // groups <= 64 (checked by the launcher)
+        for (int k = 0; k < keep; ++k) {
+            int bg = -1;
+            float bv = -INFINITY;
+            for (int g = 0; g < groups; ++g) {
+                if (kept >> g & 1ull) continue;
+                float gv = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) gv = fmaxf(gv, c[e]);
+                if (bg < 0 || gv > bv) {
+                    bg = g;
+                    bv = gv;
+                }
+            }
+            if (bg >= 0) kept |= 1ull << bg;
+        }
+        for (int g = 0; g < groups; ++g)
+            if (!(kept >> g & 1ull))
+                for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) {
+        int be = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e)
+            if (c[e] > bv) {
+                be = e;
+                bv = c[e];
+            }
+        ids[(size_t)t * top + k] = be;
+        weights[(size_t)t * top + k] = be >= 0 ? s[be] : 0.f;
+        if (be >= 0) c[be] = -INFINITY;
+    }
+}
+
+extern "C" int aie_route_topk(float* z, float* scratch, const float* corr, int T, int E, int groups, int keep, int top,
+                              int* ids, float* weights, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (E <= 0 || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 || top > E / groups * keep)
+        return AIE_BAD_ARG;
+    if (groups > 64) return AIE_UNSUPPORTED;
+    route_topk_kernel<<<(T + 63) / 64, 64, 0, st>>>(z, scratch, corr, T, E, groups, keep, top, ids, weights);
+    AIE_LAUNCH_CHECK();
+}
+
+// out[t] = sum_s weight[t, s] * (row >= 0 ? y[row] : row == -2 ? h[t] : 0),  row = pair_row[t top + s]      float32
+// (a pair marked -2 belongs to an expert that hands its input on unchanged)
+template <typename A>
+__global__ void expert_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ pair_row,
+                                               const float* __restrict__ weight, int top, const A* __restrict__ h,
+                                               float* __restrict__ out, int D) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < top; ++s) {
+            const int row = pair_row[(size_t)t * top + s];
+            const float w = weight[(size_t)t * top + s];
+            if (row >= 0) acc = fmaf(w, y[(size_t)row * D + c], acc);
+            else if (row == -2) acc = fmaf(w, to_f32<A>(h[(size_t)t * D + c]), acc);
+        }
+        out[(size_t)t * D + c] = acc;
+    }
+}
+
+extern "C" int aie_expert_combine_weighted(const float* y, const int* pair_row, const float* weight, int top,
+                                           const void* h, int h_dtype, float* out, int T, int D, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (D <= 0 || top <= 0) return AIE_BAD_ARG;
+    const int threads = D >= 1024 ? 256 : 128;
+    if (h_dtype == AIE_BF16)
+        expert_combine_weighted_kernel<bf16><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const bf16*)h, out, D);
+    else
+        expert_combine_weighted_kernel<float><<<T, threads, 0, st>>>(y, pair_row, weight, top, (const float*)h, out, D);
     AIE_LAUNCH_CHECK();
 }

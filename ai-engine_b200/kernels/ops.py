@@ -122,9 +122,13 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     return out
 
 
-def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 0) -> torch.Tensor:
-    """a[t, f] = silu(gate) * up.  block == 0: gu[t] = [gate (F) | up (F)]; block > 0: gu[t]
-    is in groups of `block` gate columns followed by their `block` up columns."""
+GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 0, activation: str = "silu") -> torch.Tensor:
+    """a[t, f] = act(gate) * up, act = silu unless `activation` names another (relu, gelu_tanh).  block == 0:
+    gu[t] = [gate (F) | up (F)]; block > 0: gu[t] is in groups of `block` gate columns followed by their `block`
+    up columns."""
     _dev(gu)
     T, F2 = gu.shape
     F = F2 // 2
@@ -133,7 +137,7 @@ def silu_mul(gu: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 
     lib = library("elementwise.cu")
     with region("silu_mul", _nb(gu, out)):
         check(lib.aie_silu_mul(_p(gu), _p(out), c_int(dtype_code(gu)), c_int(T), c_int(F), c_int(block),
-                               _stream()), "silu_mul")
+                               c_int(GLU_ACTIVATIONS[activation]), _stream()), "silu_mul")
     return out
 
 
@@ -288,17 +292,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 
 def linear_swiglu(x: torch.Tensor, w_gu: torch.Tensor, block: int = 0,
-                  err: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  err: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
     """silu(x . gate^T) * (x . up^T) for the fused gate/up weight [2F, K]; [T, F] in x's
     dtype.  block == 0: rows [0, F) are gate, [F, 2F) up.  block == 64: tiles of 64 gate
     rows + their 64 up rows, which lets the tcgen05 kernel apply the activation in its
     epilogue when the step is small."""
     if (block == TC_SWIGLU_BLOCK and x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16
-            and x.shape[0] <= TC_MAX_TOKENS and err is not None):
+            and x.shape[0] <= TC_MAX_TOKENS and err is not None and activation == "silu"):
         y = gemm_tc(x, w_gu, x.dtype, err, swiglu=True)
         if y is not None:
             return y
-    return silu_mul(linear(x, w_gu, x.dtype, err), block=block)
+    return silu_mul(linear(x, w_gu, x.dtype, err), block=block, activation=activation)
 
 
 def linear_rope_kv(x: torch.Tensor, w_qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -703,19 +707,22 @@ def gated_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> to
 EXPERT_TILE = 64         # rows per tile of the grouped products
 
 
-def expert_plan(token_ids: torch.Tensor, table: torch.Tensor, experts: int, err: torch.Tensor):
+def expert_plan(token_ids: Optional[torch.Tensor], table: torch.Tensor, experts: int, err: torch.Tensor,
+                identity: int = 0):
     """Group the (token, choice) pairs of a step by expert: (row_token [tiles * 64], pair_row [T * top],
-    tile_expert [tiles]); the sizes depend on T alone."""
+    tile_expert [tiles]); the sizes depend on T alone.  token_ids None: `table` [T, top] holds each token's
+    choices (a router's).  Choices experts .. experts + identity - 1 get no row; their pairs are marked -2."""
     _dev(token_ids, table, err)
-    T, (V, top) = token_ids.shape[0], table.shape
+    V, top = table.shape
+    T = token_ids.shape[0] if token_ids is not None else V
     tiles = (T * top + EXPERT_TILE - 1) // EXPERT_TILE + experts
-    dev = token_ids.device
+    dev = table.device
     row_token = torch.empty(tiles * EXPERT_TILE, dtype=torch.int32, device=dev)
     pair_row = torch.empty(T * top, dtype=torch.int32, device=dev)
     tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
     lib = library("sequence_ops.cu")
     check(lib.aie_expert_plan(_p(token_ids), _p(table), c_int(T), c_int(V), c_int(top), c_int(experts),
-                              c_int(EXPERT_TILE), c_int(tiles), _p(row_token), _p(pair_row), _p(tile_expert), _p(err),
+                              c_int(identity), c_int(EXPERT_TILE), c_int(tiles), _p(row_token), _p(pair_row), _p(tile_expert), _p(err),
                               _stream()), "expert_plan")
     return row_token, pair_row, tile_expert
 
@@ -816,12 +823,19 @@ def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table
 
 def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_tok: Optional[torch.Tensor],
                       decay_head: Optional[torch.Tensor], q_scale: float, k_scale: float, state: torch.Tensor,
-                      ctx, H: int, d: int, dv: int) -> torch.Tensor:
+                      ctx, H: int, d: int, dv: int, heads_per_group: int = 1, dt_raw: Optional[torch.Tensor] = None,
+                      dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
+                      skip: Optional[torch.Tensor] = None) -> torch.Tensor:
     """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens, the state
     [max_seqs, H, d, dv] float32 read and left in each request's slot.  q, k [T, H * d] and v [T, H * dv] are
     float32 views with one row stride; decay_tok [T, H * d] float32 (rows any stride) or decay_head [H].
-    Returns o [T, H, dv] float32."""
-    _dev(state, decay_head)
+    With `dt_raw` [T, H] (a float32 view, rows any stride), dt_bias and a_log [H]: the decay is one number per
+    token and head, a = exp(-exp(a_log) dt) with dt = softplus(dt_raw + dt_bias), and v is scaled by dt.
+    heads_per_group: neighbouring heads that share one head of q and k ([T, H / heads_per_group * d]).
+    skip [H]: skip[h] * v is added to the output.  Returns o [T, H, dv] float32."""
+    _dev(state, decay_head, dt_bias, a_log, skip)
+    if dt_raw is not None and (dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_bias is None or a_log is None):
+        raise KernelError("linear_recurrence: step sizes are a float32 view with their bias and rates")
     T = q.shape[0]
     ld = q.stride(0)
     if (q.dtype != torch.float32 or k.dtype != torch.float32 or v.dtype != torch.float32 or k.stride(0) != ld
@@ -834,7 +848,9 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                                         c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
                                         c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),
                                         _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
-                                        c_int(state.shape[0]), _p(ctx.err), _stream()), "linear_recurrence")
+                                        c_int(state.shape[0]), _p(ctx.err), c_int(heads_per_group), _p(dt_raw),
+                                        c_int(dt_raw.stride(0) if dt_raw is not None else 0), _p(dt_bias), _p(a_log),
+                                        _p(skip), _stream()), "linear_recurrence")
     return out
 
 
@@ -868,3 +884,112 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_w: torch.Tensor, out_d
                                           _stream()), "gemm_tc_grouped")
         return out
     return gemm_f32_ex(x, w, out, rows, N, K, K, N, w_bs=N * K, a_rows=row_src, tile_w=tile_w)
+
+
+# ---------------------------------------------------------------------------
+# parts of layers with a convolved projection, a state space, a router, bounded logits
+def causal_conv(u: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, ctx,
+                out_dtype: torch.dtype, activation: Optional[str] = None, residual: bool = False,
+                dup_from: int = 0, dup_n: int = 0) -> torch.Tensor:
+    """y_t = (u_t +) bias + sum_j w[:, j] u_(t - taps + 1 + j) per channel over each request's tokens, then the
+    activation (None | "silu").  u: a float32 view [T, C] with any row stride (a slice of a wider projection);
+    w [C, taps], bias [C] or None, float32; state [max_seqs, taps - 1, C] float32: each request's last taps - 1
+    inputs.  The last dup_n channels (from dup_from on) are written twice, the copy dup_n columns further on:
+    the result is [T, C + dup_n]."""
+    _dev(w, bias, state)
+    T, C = u.shape
+    taps = w.shape[1]
+    if (u.dtype != torch.float32 or u.stride(1) != 1 or w.dtype != torch.float32 or state.dtype != torch.float32
+            or (bias is not None and bias.dtype != torch.float32)):
+        raise KernelError("causal_conv: inputs, taps, bias and state are float32")
+    if w.shape[0] != C or state.shape[1:] != (max(taps - 1, 0), C) or (bias is not None and bias.shape != (C,)):
+        raise KernelError("causal_conv: shapes do not fit")
+    if activation not in (None, "silu"):
+        raise KernelError(f"causal_conv: activation `{activation}` is not known (silu)")
+    out = torch.empty((T, C + dup_n), dtype=out_dtype, device=u.device)
+    lib = library("sequence_ops.cu")
+    with region("causal_conv", T * C * 4 + _nb(out)):
+        check(lib.aie_causal_conv(_p(u), c_int(u.stride(0)), _p(w), _p(bias), _p(state), _p(out), c_int(dtype_code(out)),
+                                  c_int(out.stride(0)), _p(ctx.q_start), _p(ctx.q_len), _p(ctx.slots), _p(ctx.token_req),
+                                  c_int(T), c_int(C), c_int(taps), c_int(1 if residual else 0),
+                                  c_int(1 if activation == "silu" else 0), c_int(dup_from), c_int(dup_n),
+                                  c_int(state.shape[0]), _p(ctx.err), _stream()), "causal_conv")
+    return out
+
+
+def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+    """g = y * silu(z); each of `parts` equal parts of a row is divided by its own root mean square; times weight.
+    y [T, W] float32; z a float32 view [T, W] with any row stride; weight [W] float32."""
+    _dev(y, weight)
+    T, W = y.shape
+    if (y.dtype != torch.float32 or z.dtype != torch.float32 or z.shape != (T, W) or z.stride(1) != 1
+            or weight.dtype != torch.float32 or weight.shape != (W,) or parts < 1 or W % parts):
+        raise KernelError("gate_group_norm: shapes or dtypes do not fit")
+    out = torch.empty((T, W), dtype=out_dtype, device=y.device)
+    lib = library("sequence_ops.cu")
+    with region("gate_group_norm", 2 * _nb(y) + _nb(out)):
+        check(lib.aie_gate_group_norm(_p(y), _p(z), c_int(z.stride(0)), _p(weight), _p(out), c_int(dtype_code(out)),
+                                      c_int(T), c_int(W), c_int(parts), c_float(eps), _stream()), "gate_group_norm")
+    return out
+
+
+def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int):
+    """A router's choice per token from float32 logits [T, E] (overwritten by their softmax): the `top` outputs
+    with the largest softmax + correction among the members of the `keep` groups (of `groups` equal groups of
+    neighbours) whose best member is largest.  Returns (ids int32 [T, top], weights float32 [T, top]: the
+    chosen outputs' softmax)."""
+    _dev(logits, correction)
+    T, E = logits.shape
+    if logits.dtype != torch.float32 or (correction is not None and (correction.dtype != torch.float32 or
+                                                                    correction.shape != (E,))):
+        raise KernelError("route_topk: float32 logits and correction")
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    scratch = torch.empty_like(logits)
+    lib = library("sequence_ops.cu")
+    with region("route_topk", 3 * _nb(logits)):
+        check(lib.aie_route_topk(_p(logits), _p(scratch), _p(correction), c_int(T), c_int(E), c_int(groups), c_int(keep),
+                                 c_int(top), _p(ids), _p(weights), _stream()), "route_topk")
+    return ids, weights
+
+
+def expert_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_s weights[t, s] * y[pair_row[t top + s]], a pair marked -2 standing for h[t] itself; float32
+    [T, D].  y [rows, D] float32; weights [T, top] float32; h [T, D] in the compute dtype."""
+    _dev(y, pair_row, weights, h)
+    T, top = weights.shape
+    D = h.shape[1]
+    if y.dtype != torch.float32 or weights.dtype != torch.float32 or y.shape[1] != D or pair_row.numel() != T * top:
+        raise KernelError("expert_combine_weighted: shapes or dtypes do not fit")
+    out = torch.empty((T, D), dtype=torch.float32, device=y.device)
+    lib = library("sequence_ops.cu")
+    with region("expert_combine", (top + 2) * T * D * 4):
+        check(lib.aie_expert_combine_weighted(_p(y), _p(pair_row), _p(weights), c_int(top), _p(h), c_int(dtype_code(h)),
+                                              _p(out), c_int(T), c_int(D), _stream()), "expert_combine_weighted")
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _dev(x)
+    if x.dtype != torch.float32:
+        raise KernelError("softcap: float32 logits")
+    lib = library("elementwise.cu")
+    with region("softcap", 2 * _nb(x)):
+        check(lib.aie_softcap(_p(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
+    return x
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.Tensor:
+    """sa * a + sb * b in float32; a and b [T, D], or [parts, T, D] (the parts of a split product are added first)."""
+    _dev(a, b)
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape[-2:] != b.shape[-2:]:
+        raise KernelError("scaled_sum: float32 operands of one shape")
+    out = torch.empty(a.shape[-2:], dtype=torch.float32, device=a.device)
+    lib = library("elementwise.cu")
+    with region("scaled_sum", _nb(a, b, out)):
+        check(lib.aie_scaled_sum(_p(a), c_int(a.shape[0] if a.dim() == 3 else 1), c_float(sa), _p(b),
+                                 c_int(b.shape[0] if b.dim() == 3 else 1), c_float(sb), _p(out),
+                                 c_longlong(out.numel()), _stream()), "scaled_sum")
+    return out

@@ -1,2 +1,3 @@
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import pifutar  # noqa: F401  (registers Pifutar)
+from . import zupitar  # noqa: F401  (registers Zupitar)

@@ -1,13 +1,15 @@
 from .attention import ATTENTION_WORK, AttentionWork, GQAAttention
 from .base import (Block, BuildEnv, CacheNeed, FeedForward, KVRequest, LayerCache, Mixer, Norm, Part,
                    PositionEncoding, StateRequest, StepPlanner, TokenFilter)
-from .block import DepthAveragedBlock, PreNormBlock
+from .block import DepthAveragedBlock, PreNormBlock, SandwichNormBlock
 from .conv import CausalShortConv
 from .embedding import LMHead, TokenEmbedding
 from .latent_attention import LATENT_WORK, LatentAttention, LatentWork
 from .linear_attention import DecayLinearAttention
 from .mlp import PolyNormFF, SwiGLU
-from .moe import TableMoE
+from .moe import RoutedMoE, TableMoE
+from .parallel import ParallelMixers
+from .state_space import ScalarDecayStateSpace
 from .model import Layer, Model, tensor_specs_of
 from .norm import RMSNorm
 from .registry import (lookup, register, register_block, register_feed_forward, register_mixer,
@@ -28,6 +30,10 @@ register("feed_forward", "polynorm_ff", PolyNormFF)
 register("feed_forward", "table_moe", TableMoE)
 register("filter", "causal_short_conv", CausalShortConv)
 register("block", "prenorm_depth_average", DepthAveragedBlock)
+register("block", "sandwich_norm", SandwichNormBlock)
+register("mixer", "parallel_mixers", ParallelMixers)
+register("mixer", "scalar_decay_state_space", ScalarDecayStateSpace)
+register("feed_forward", "routed_moe", RoutedMoE)
 
 __all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv", "CacheNeed", "FeedForward",
            "KVRequest", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding", "StateRequest", "StepPlanner", "PreNormBlock", "LMHead",
@@ -35,4 +41,5 @@ __all__ = ["ATTENTION_WORK", "AttentionWork", "GQAAttention", "Block", "BuildEnv
            "register", "register_block", "register_feed_forward", "register_mixer",
            "register_norm", "register_position_encoding", "RotaryEncoding", "rotary_inv_freq",
            "LayerSpec", "ModelSpec", "PartSpec", "RunStep", "TokenFilter", "DepthAveragedBlock", "CausalShortConv",
-           "LatentAttention", "DecayLinearAttention", "PolyNormFF", "TableMoE"]
+           "LatentAttention", "DecayLinearAttention", "PolyNormFF", "TableMoE", "SandwichNormBlock", "ParallelMixers",
+           "ScalarDecayStateSpace", "RoutedMoE"]

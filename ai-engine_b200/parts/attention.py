@@ -17,7 +17,7 @@ import numpy as np
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import KVRequest, Mixer, StepPlanner
+from .base import KVRequest, Mixer, StateRequest, StepPlanner
 
 
 class AttentionWork(StepPlanner):
@@ -51,7 +51,12 @@ class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all
     keys), scale (None = 1/sqrt(head_dim)), position_encoding (name of a rotary
     encoding of the model, or None).  tensors: q, k, v [heads*d, hidden], o
-    [hidden, H*d].  q, k, v are fused into one [(H + 2K) * d, hidden] weight at load."""
+    [hidden, H*d].  q, k, v are fused into one [(H + 2K) * d, hidden] weight at load.
+
+    Two more params: `qk_conv` (taps; 0: none): the projected queries and keys pass a causal convolution over
+    time per channel (tensors q_conv [H d, taps], k_conv [K d, taps], no bias, no activation) before they are
+    rotated; the last taps - 1 projected rows of a request are state in its slot.  `tied_values`: there is no
+    value projection, a token's value is its key as it is before the rotation."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -71,29 +76,47 @@ class GQAAttention(Mixer):
             raise ValueError("attention: its kernels rotate split halves; an interleaved encoding is not taken")
         if rot is not None and rot[1] > self.d:
             raise ValueError("attention: rotary width exceeds head_dim")
-        self.w_qkv = self.w_o = None
+        self.taps = int(p.get("qk_conv") or 0)
+        self.tied = bool(p.get("tied_values"))
+        if self.taps and not self.tied:
+            raise ValueError("attention: a convolution of queries and keys is built for tied values only")
+        if self.tied and not self.taps:
+            raise ValueError("attention: tied values are built behind a convolution (qk_conv >= 1) only")
+        self.w_qkv = self.w_o = self.w_conv = None
         self._no_rope = None
 
     def tensor_specs(self):
         t = self.spec.tensors
-        return [TensorSpec(t["q"], (self.H * self.d, self.hidden)),
-                TensorSpec(t["k"], (self.K * self.d, self.hidden)),
-                TensorSpec(t["v"], (self.K * self.d, self.hidden)),
-                TensorSpec(t["o"], (self.hidden, self.H * self.d))]
+        specs = [TensorSpec(t["q"], (self.H * self.d, self.hidden)),
+                 TensorSpec(t["k"], (self.K * self.d, self.hidden))]
+        if not self.tied:
+            specs.append(TensorSpec(t["v"], (self.K * self.d, self.hidden)))
+        specs.append(TensorSpec(t["o"], (self.hidden, self.H * self.d)))
+        if self.taps:
+            specs += [TensorSpec(t["q_conv"], (self.H * self.d, self.taps), std=0.4),
+                      TensorSpec(t["k_conv"], (self.K * self.d, self.taps), std=0.4)]
+        return specs
 
     def load(self, source):
         t = self.spec.tensors
-        q, k, v = source.get(t["q"]), source.get(t["k"]), source.get(t["v"])
-        dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
-        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        ws = [source.get(t["q"]), source.get(t["k"])] + ([] if self.tied else [source.get(t["v"])])
+        dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.w_o = source.get(t["o"])
+        if self.taps:
+            self.w_conv = torch.cat([source.get(t["q_conv"]).float(), source.get(t["k_conv"]).float()], dim=0).contiguous()
         self._no_rope = torch.zeros(0, dtype=torch.float32, device=self.env.device)
+
+    def state_request(self):
+        if not self.taps:
+            return None
+        return StateRequest((self.taps - 1, (self.H + self.K) * self.d), torch.float32)
 
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
 
     def flops(self, tokens, keys=0.0):
-        proj = 2.0 * tokens * self.hidden * (2 * self.H + 2 * self.K) * self.d
+        proj = 2.0 * tokens * self.hidden * (2 * self.H + (1 if self.tied else 2) * self.K) * self.d
         return proj + 4.0 * tokens * keys * self.H * self.d         # q.k and p.v
 
     def cache_request(self):
@@ -107,10 +130,21 @@ class GQAAttention(Mixer):
     def forward(self, h, ctx, cache, add_to=None):
         rot = self.rope.rotation() if self.rope is not None else None
         inv_freq = rot[0] if rot is not None else self._no_rope
-        # a small bfloat16 step: product, rotation and cache write in one kernel
-        q = ops.linear_rope_kv(h, self.w_qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
-                               cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
-                               write=cache.writes)
+        q = None
+        if self.taps:
+            # queries and keys through their convolution in float32; the keys' columns are written twice, so that
+            # the row is [q | k | v = k] and the second copy reaches the cache unrotated
+            qk = ops.linear(h, self.w_qkv, torch.float32, ctx.err)
+            qkv = ops.causal_conv(qk, self.w_conv, None, cache.state, ctx, torch.float32,
+                                  dup_from=self.H * self.d, dup_n=self.K * self.d)
+            q = ops.rope_kv_write(qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
+                                  cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
+                                  write=cache.writes)
+        else:
+            # a small bfloat16 step: product, rotation and cache write in one kernel
+            q = ops.linear_rope_kv(h, self.w_qkv, cache.k_pages, cache.v_pages, ctx.positions, ctx.token_req,
+                                   cache.block_table, inv_freq, self.H, self.K, self.d, ctx.err,
+                                   write=cache.writes)
         if q is None:
             # the projection reaches the rotation in float32 whatever the step's size (unjoined parts of a
             # small step, the library product's float32 output of a large one): q and k are rounded to

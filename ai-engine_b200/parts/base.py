@@ -44,12 +44,13 @@ class StateRequest:
 @dataclass(frozen=True)
 class CacheNeed:
     """What one part of one run-order entry asks of the cache manager: pages (`kv`), a
-    slot-indexed state tensor (`state`), or another run's pages read without writing
-    (`cache_from`: the index of that run-order entry; `kv` is None then)."""
+    slot-indexed state tensor (`state`; a dict name -> StateRequest for a part that keeps several), or another
+    run's pages read without writing (`cache_from`: the index of that run-order entry; `kv` is None then).
+    The role of a part inside a composite part is `<role>.<name>`."""
     run: int
     role: str
     kv: Optional[KVRequest] = None
-    state: Optional[StateRequest] = None
+    state: object = None                      # StateRequest | Dict[str, StateRequest] | None
     cache_from: Optional[int] = None
 
 
@@ -76,7 +77,9 @@ class LayerCache:
     block_table: Optional[torch.Tensor] = None   # int32 [R, width], row r = request r of the batch
     page_size: int = 0
     writes: bool = True                          # False: the pages belong to another run; read only
-    state: Optional[torch.Tensor] = None         # [max_seqs, *shape], row = the request's slot
+    state: object = None                         # [max_seqs, *shape], row = the request's slot; a dict of such
+    #                                              tensors by name for a part that asked for several
+    children: Optional[Dict[str, "LayerCache"]] = None   # of a composite part: its parts' caches by name
 
 
 class Part:
@@ -102,13 +105,34 @@ class Part:
         """Pages this part wants (any part of a block may ask, not only the one in the role `mixer`)."""
         return None
 
-    def state_request(self) -> Optional[StateRequest]:
-        """Per-request state of fixed size this part wants."""
+    def state_request(self):
+        """Per-request state of fixed size this part wants: a StateRequest, or a dict name -> StateRequest for
+        several tensors (the part then finds a dict of tensors under `LayerCache.state`)."""
         return None
+
+    def sub_parts(self) -> Dict[str, "Part"]:
+        """The parts a composite part is made of, by name (each may ask for pages, state and a planner of its
+        own; it gets its cache as `cache.children[name]`).  The composite loads them and reports their tensors,
+        bytes and operations itself."""
+        return {}
 
     def step_planner(self) -> Optional[StepPlanner]:
         """The planner whose lists this part reads in forward (None: the generic arrays suffice)."""
         return None
+
+
+def walk(part: "Part"):
+    """`part` and, recursively, the parts it is made of."""
+    yield part
+    for child in part.sub_parts().values():
+        yield from walk(child)
+
+
+def walk_named(role: str, part: "Part"):
+    """(role, part) for `part` and its parts; a child's role is `<role>.<name>`."""
+    yield role, part
+    for name, child in part.sub_parts().items():
+        yield from walk_named(f"{role}.{name}", child)
 
 
 class Mixer(Part):

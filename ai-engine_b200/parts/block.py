@@ -96,3 +96,38 @@ class DepthAveragedBlock(Block):
             return x, a
         ops.depth_average(x, a, history, self.coef, self.depth + 1)
         return x, None
+
+
+class SandwichNormBlock(Block):
+    """A block that normalises each sublayer's input and its output:
+
+        x = x + post_norm(mixer(norm(x)));   x = x + ffn_post_norm(ffn(ffn_norm(x)))
+
+    The feed-forward with its two norms is optional.  A post-norm reads the branch in float32 and hands its
+    float32 result on as the pending branch, which the next norm adds to the stream."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
+             "ffn_norm": "norm", "ffn": "feed_forward", "ffn_post_norm": "norm"}
+    optional_roles = ("ffn_norm", "ffn", "ffn_post_norm")
+
+    def __init__(self, spec, env, parts):
+        super().__init__(spec, env)
+        self.p = parts
+        if ("ffn" in parts) != ("ffn_norm" in parts) or ("ffn" in parts) != ("ffn_post_norm" in parts):
+            raise ValueError("sandwich block: a feed-forward comes with both of its norms")
+
+    @staticmethod
+    def _normed(norm, y):
+        """norm(y) in float32 for a branch y [T, D] (any dtype) or float32 [parts, T, D] (summed first)."""
+        if y.dim() == 3:
+            return norm.forward(y[0], y[1:] if y.shape[0] > 1 else None, write_back=False)
+        return norm.forward(ops.cast(y, torch.float32), None, write_back=False)
+
+    def forward(self, x, pending, ctx, caches):
+        h = self.p["mixer_norm"].forward(x, pending)
+        pending = self._normed(self.p["mixer_post_norm"], self.p["mixer"].forward(h, ctx, caches.get("mixer")))
+        ffn = self.p.get("ffn")
+        if ffn is not None:
+            h = self.p["ffn_norm"].forward(x, pending)
+            pending = self._normed(self.p["ffn_post_norm"], ffn.forward(h, ctx))
+        return x, pending

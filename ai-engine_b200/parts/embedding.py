@@ -32,13 +32,16 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
-    """params: vocab_size, hidden_size, alternatives, stored.  tensors: weight
-    [vocab, hidden] (the embedding's name when tied).  forward(h [N, hidden]) ->
-    float32 logits [N, vocab]."""
+    """params: vocab_size, hidden_size, alternatives, stored, softcap (0 or absent: none; c > 0: the logits
+    become c * tanh(logits / c)).  tensors: weight [vocab, hidden] (the embedding's name when tied).
+    forward(h [N, hidden]) -> float32 logits [N, vocab]."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.softcap = float(spec.params.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ValueError(f"head: softcap must be positive, got {self.softcap}")
         self.weight = None
 
     def tensor_specs(self):
@@ -56,4 +59,5 @@ class LMHead(Part):
         return 2.0 * tokens * self.vocab * self.hidden
 
     def forward(self, h, err=None):
-        return ops.linear(h, self.weight, torch.float32, err)
+        logits = ops.linear(h, self.weight, torch.float32, err)
+        return ops.softcap(logits, self.softcap) if self.softcap else logits

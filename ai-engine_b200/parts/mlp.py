@@ -10,13 +10,18 @@ from .base import FeedForward
 
 
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size.  tensors: gate, up [F, hidden],
-    down [hidden, F].  gate and up are fused into one [2F, hidden] weight at load."""
+    """params: hidden_size, intermediate_size, activation (default "silu"; "relu" and "gelu_tanh" give
+    down(act(gate(x)) * up(x)) with that act).  tensors: gate, up [F, hidden], down [hidden, F].  gate and up
+    are fused into one [2F, hidden] weight at load."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation") or "silu"
+        if self.activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: activation `{self.activation}` is not known "
+                             f"({', '.join(ops.GLU_ACTIVATIONS)})")
         self.w_gu = self.w_down = None
         self.block = 0
 
@@ -32,7 +37,8 @@ class SwiGLU(FeedForward):
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         # bfloat16: 64 gate rows then their 64 up rows, tile by tile, so that a 128-row
         # weight tile of the tensor-core kernel holds both halves of 64 outputs
-        self.block = ops.TC_SWIGLU_BLOCK if (dt == torch.bfloat16 and self.inter % ops.TC_SWIGLU_BLOCK == 0) else 0
+        self.block = ops.TC_SWIGLU_BLOCK if (dt == torch.bfloat16 and self.inter % ops.TC_SWIGLU_BLOCK == 0
+                                             and self.activation == "silu") else 0
         if self.block:
             b = self.block
             self.w_gu = torch.stack([g.view(-1, b, self.hidden), u.view(-1, b, self.hidden)], dim=1) \
@@ -51,7 +57,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx, add_to=None):
         err = ctx.err if ctx is not None else None
-        a = ops.linear_swiglu(h, self.w_gu, self.block, err)
+        a = ops.linear_swiglu(h, self.w_gu, self.block, err, self.activation)
         if add_to is not None and ops.linear_add(add_to, a, self.w_down):
             return None
         return ops.linear_parts(a, self.w_down, err)   # joins the residual in float32, inside the next norm

@@ -11,7 +11,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..weights.loader import TensorSpec, WeightSource
-from .base import BuildEnv, CacheNeed, Part, StepPlanner
+from .base import BuildEnv, CacheNeed, Part, StepPlanner, walk, walk_named
 from .registry import lookup
 from .spec import LayerSpec, ModelSpec, PartSpec
 
@@ -35,10 +35,11 @@ class Layer:
     def cache_needs(self):
         """(role, pages wanted, state wanted) of every part that asks for either."""
         out = []
-        for role, part in self.parts.items():
-            kv, st = part.cache_request(), part.state_request()
-            if kv is not None or st is not None:
-                out.append((role, kv, st))
+        for top_role, top_part in self.parts.items():
+            for role, part in walk_named(top_role, top_part):
+                kv, st = part.cache_request(), part.state_request()
+                if kv is not None or st is not None:
+                    out.append((role, kv, st))
         return out
 
 
@@ -109,10 +110,11 @@ class Model:
     def step_planners(self) -> List[StepPlanner]:
         """The planners whose lists the parts read in forward, each once."""
         out: List[StepPlanner] = []
-        for p in self.all_parts():
-            pl = p.step_planner()
-            if pl is not None and all(pl is not q for q in out):
-                out.append(pl)
+        for top in self.all_parts():
+            for p in walk(top):
+                pl = p.step_planner()
+                if pl is not None and all(pl is not q for q in out):
+                    out.append(pl)
         return out
 
     def keeps_state(self) -> bool:
@@ -122,12 +124,12 @@ class Model:
         """Whether decode steps may be rounded up by repeating a row: every part that keeps state
         skips rows with `ctx.live == 0`."""
         return all(getattr(p, "skips_padded_rows", False) or p.state_request() is None
-                   for l in self.layers for p in l.parts.values())
+                   for l in self.layers for top in l.parts.values() for p in walk(top))
 
     def has_host_parts(self) -> bool:
         """True when a part reads step data on the host inside forward (`host_side =
         True` on its class): such a model cannot be replayed from a captured graph."""
-        return any(getattr(p, "host_side", False) for p in self.all_parts())
+        return any(getattr(p, "host_side", False) for top in self.all_parts() for p in walk(top))
 
     def step_flops(self, tokens: int, keys: float = 0.0, logit_rows: int = 1) -> float:
         """Floating-point operations of one step of `tokens` tokens that read `keys` cached positions

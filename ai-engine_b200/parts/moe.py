@@ -1,4 +1,8 @@
-"""A mixture of small gated feed-forwards whose experts are chosen by a table, not by a router: row `id` of the
+"""Mixtures of small gated feed-forwards.  `TableMoE`: the experts are chosen by a table, not by a router;
+`RoutedMoE` (below): by a softmax router with a correction for the choice, groups of experts, and experts that
+hand their input on unchanged.
+
+TableMoE: row `id` of the
 table [vocab, top] names the experts of a token with that id, each weighing 1 / top.  An expert is
 
     g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit),  y = g * sigmoid(alpha g) * (u + shift),  W_down y
@@ -85,3 +89,76 @@ class TableMoE(FeedForward):
             shared = ops.linear(sa, self.w_shared_down, torch.float32, ctx.err)
             gate = sp[:, 2 * self.Fs]
         return ops.expert_combine(y, pair_row, self.top, 1.0 / self.top, shared, gate, T)
+
+
+class RoutedMoE(FeedForward):
+    """A mixture of gated feed-forwards W_down (act(W_gate h) * (W_up h)) chosen by a router, per token:
+
+        s = softmax(W_router h)                     over all router outputs, float32
+        choice = s + correction                     only the choice uses the correction
+        the outputs form `groups` equal groups of neighbours; a group counts as its best choice value, and only
+        members of the `keep` best groups can be chosen; the `top` largest choice values among them are taken
+        out = sum over the chosen e of s_e * expert_e(h)            (the weights are not renormalised)
+
+    The router's last `identity` outputs have no tensors: such an expert's output is h itself.
+
+    params: hidden_size, num_experts (with tensors), identity (default 0), top, intermediate_size, groups
+    (default 1), keep (default 1), activation (default "silu").  tensors: router [num_experts + identity, hidden],
+    correction [num_experts + identity]; gate, up, down as patterns with `{e}` for the expert's index."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.E, self.ident = int(p["hidden_size"]), int(p["num_experts"]), int(p.get("identity") or 0)
+        self.top, self.F = int(p["top"]), int(p["intermediate_size"])
+        self.groups, self.keep = int(p.get("groups") or 1), int(p.get("keep") or 1)
+        self.activation = p.get("activation") or "silu"
+        total = self.E + self.ident
+        if self.activation != "silu":
+            raise ValueError("routed experts: the experts' activation is silu")
+        if total % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= total // self.groups * self.keep:
+            raise ValueError(f"routed experts: {total} router outputs do not divide into {self.groups} groups of which "
+                             f"{self.keep} are kept for {self.top} choices")
+        self.w_router = self.correction = self.w_gu = self.w_down = None
+
+    def tensor_specs(self):
+        t, D, total = self.spec.tensors, self.hidden, self.E + self.ident
+        specs = [TensorSpec(t["router"], (total, D), std=0.3), TensorSpec(t["correction"], (total,), std=0.05)]
+        for e in range(self.E):
+            specs += [TensorSpec(t["gate"].format(e=e), (self.F, D)), TensorSpec(t["up"].format(e=e), (self.F, D)),
+                      TensorSpec(t["down"].format(e=e), (D, self.F))]
+        return specs
+
+    def load(self, source):
+        t = self.spec.tensors
+        self.w_router = source.get(t["router"])
+        self.correction = source.get(t["correction"]).float().contiguous()
+        gu, down = [], []
+        for e in range(self.E):
+            gu += [source.get(t["gate"].format(e=e)), source.get(t["up"].format(e=e))]
+            down.append(source.get(t["down"].format(e=e)))
+        if self.E:
+            dt = torch.float32 if any(w.dtype == torch.float32 for w in gu + down) else gu[0].dtype
+            self.w_gu = torch.stack([w.to(dt) for w in gu]).view(self.E, 2 * self.F, self.hidden).contiguous()
+            self.w_down = torch.stack([w.to(dt) for w in down]).contiguous()              # [E, hidden, F]
+
+    def weight_bytes(self):
+        """What a step of many tokens reads: every expert once."""
+        return sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gu, self.w_down) if w is not None)
+
+    def flops(self, tokens, keys=0.0):
+        return 2.0 * tokens * self.hidden * (3 * self.top * self.F + self.E + self.ident)
+
+    def forward(self, h, ctx):
+        # the router in float32 on the sublayer's input as the experts see it
+        logits = ops.gemm_f32(ops.cast(h, torch.float32), self.w_router)
+        ids, weights = ops.route_topk(logits, self.correction, self.groups, self.keep, self.top)
+        if not self.E:
+            y = torch.zeros((1, self.hidden), dtype=torch.float32, device=h.device)
+            pair_row = torch.full((ids.numel(),), -2, dtype=torch.int32, device=h.device)
+            return ops.expert_combine_weighted(y, pair_row, weights, h)
+        row_token, pair_row, tile_expert = ops.expert_plan(None, ids, self.E, ctx.err, identity=self.ident)
+        gu = ops.grouped_linear(h, self.w_gu, tile_expert, torch.float32, ctx.err, row_src=row_token)
+        act = ops.clamped_glu(gu, self.F, float("inf"), 1.0, 0.0, self.env.dtype)       # silu(gate) * up
+        y = ops.grouped_linear(act, self.w_down, tile_expert, torch.float32, ctx.err)
+        return ops.expert_combine_weighted(y, pair_row, weights, h)

@@ -5,7 +5,7 @@ Default (crates/ai-engine-runtime/src/arch/rope.rs:34-36): inv_freq[i] =
 max_position_embeddings; here only inv_freq is kept and kernels compute
 cos/sin(float(pos) * inv_freq[i]) in float32, so no table bounds the context.
 
-`llama3` scaling is not in the reference (it reads no rope_scaling); it follows
+`linear` scaling divides every frequency by `factor`.  `llama3` scaling is not in the reference (it reads no rope_scaling); it follows
 the rule the config keys name: with wavelength = 2*pi / inv_freq, frequencies
 whose wavelength is below original/high_freq_factor are kept, above
 original/low_freq_factor are divided by `factor`, and between the two are
@@ -28,8 +28,10 @@ def rotary_inv_freq(rot_dim: int, theta: float, scaling=None) -> np.ndarray:
     if not scaling:
         return base
     kind = scaling.get("rope_type", scaling.get("type"))
+    if kind == "linear":         # every frequency divided by the factor: positions stretched evenly
+        return (base.astype(np.float64) / float(scaling["factor"])).astype(np.float32)
     if kind != "llama3":
-        raise ValueError(f"rotary scaling `{kind}` is not supported (supported: llama3)")
+        raise ValueError(f"rotary scaling `{kind}` is not supported (supported: llama3, linear)")
     factor = float(scaling["factor"])
     low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
     original = float(scaling["original_max_position_embeddings"])
@@ -44,7 +46,7 @@ def rotary_inv_freq(rot_dim: int, theta: float, scaling=None) -> np.ndarray:
 
 class RotaryEncoding(PositionEncoding):
     """params: rot_dim (elements of each head that are rotated; the full head for
-    Llama), theta, scaling (None or the llama3 dict), layout ("halves", the default: element i turns with
+    Llama), theta, scaling (None, the llama3 dict, or {"type": "linear", "factor": f}), layout ("halves", the default: element i turns with
     element i + rot_dim / 2; "interleaved": element 2i with 2i + 1; a mixer reads `interleaved`).  Holds
     inv_freq [rot_dim / 2] float32 on the device."""
 

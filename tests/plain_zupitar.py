@@ -38,10 +38,11 @@ def gated_ff(h, w_gate, w_up, w_down, act):
     return (act(h @ w_gate.T) * (h @ w_up.T)) @ w_down.T
 
 
-def route(h, w_router, correction, top, group_count, group_keep):
+def route(h, w_router, correction, top, group_count, group_keep, margins=None):
     """(chosen expert ids [T, top], weights [T, top]).  Scores are a softmax over all router outputs; the choice
     is made on score + correction among the members of the `group_keep` groups whose best member is largest;
-    the weights are the plain scores of the chosen ones."""
+    the weights are the plain scores of the chosen ones.  `margins`: a list that receives, per token, how far the
+    choice is from turning (the last chosen value above the first one left out, for experts and for groups)."""
     s = torch.softmax(h @ w_router.T, dim=-1)
     choice = s + correction
     T, E = s.shape
@@ -51,13 +52,22 @@ def route(h, w_router, correction, top, group_count, group_keep):
     kept.scatter_(1, best.topk(group_keep, dim=-1).indices, True)
     masked = torch.where(kept.repeat_interleave(per, dim=1), choice, torch.full_like(choice, -math.inf))
     ids = masked.topk(top, dim=-1).indices
+    if margins is not None:
+        m = torch.full((T,), math.inf, dtype=s.dtype)
+        if top < per * group_keep:
+            srt = masked.sort(dim=-1, descending=True).values
+            m = torch.minimum(m, srt[:, top - 1] - srt[:, top])
+        if group_keep < group_count:
+            srt = best.sort(dim=-1, descending=True).values
+            m = torch.minimum(m, srt[:, group_keep - 1] - srt[:, group_keep])
+        margins.append(m)
     return ids, s.gather(1, ids)
 
 
-def routed_moe(h, w_router, correction, experts, identity, top, group_count, group_keep):
+def routed_moe(h, w_router, correction, experts, identity, top, group_count, group_keep, margins=None):
     """`experts`: list of (gate, up, down); the router's last `identity` outputs stand for experts that hand
     their input on unchanged."""
-    ids, w = route(h, w_router, correction, top, group_count, group_keep)
+    ids, w = route(h, w_router, correction, top, group_count, group_keep, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -193,8 +203,10 @@ def _sub(tensors, prefix, dtype):
 
 
 def forward(cfg: dict, tensors: Dict[str, torch.Tensor], ids: List[int], dtype=torch.float64,
-            state: Optional[State] = None, layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [len(ids), vocab] of the tokens `ids`, continuing `state` when given (it is updated)."""
+            state: Optional[State] = None, layers_out: Optional[list] = None,
+            margins_out: Optional[list] = None) -> torch.Tensor:
+    """Logits [len(ids), vocab] of the tokens `ids`, continuing `state` when given (it is updated).  `layers_out`
+    receives the stream after every layer, `margins_out` every router's margins (see `route`)."""
     st = state if state is not None else State(cfg, dtype)
     eps = float(cfg["norm"]["eps"])
     W = lambda name: tensors[name].to(dtype)
@@ -220,8 +232,9 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], ids: List[int], dtype=t
                 r = f["router"]
                 experts = [(W(f"{p}mlp.e{e}.gate"), W(f"{p}mlp.e{e}.up"), W(f"{p}mlp.e{e}.down"))
                            for e in range(r["experts"])]
+                groups = r.get("groups") or dict(count=1, keep=1)
                 y = routed_moe(h, W(p + "mlp.router"), W(p + "mlp.correction"), experts, r.get("identity", 0),
-                               r["top"], r["groups"]["count"], r["groups"]["keep"])
+                               r["top"], groups["count"], groups["keep"], margins_out)
             x = x + norm(y, W(p + "norm2b"), eps)
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -28,10 +28,11 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
                          const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ slots,
                          int H, int d, int dv, int lanes, int groups, int TT, int max_slots, int vec, int vec4, unsigned* err,
                          int hpg, const float* __restrict__ dt_raw, int ld_dt, const float* __restrict__ dt_bias,
-                         const float* __restrict__ a_log, const float* __restrict__ skip) {
+                         const float* __restrict__ a_log, const float* __restrict__ skip, int max_len) {
     extern __shared__ __align__(16) float lr_sm[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bg = blockIdx.x % groups, h = (blockIdx.x / groups) % H, r = blockIdx.x / (groups * H);
+    if (max_len > 0 && q_len[r] > max_len) return;               // a longer portion is another kernel's
     const int slot = slots[r];
     if (slot < 0 || slot >= max_slots) {
         if (tid == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
@@ -156,11 +157,12 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
 // k_scale, the output by q_scale (both 1 or d^-1/2).  state [max_slots, H, d, dv]; out [T, H, dv].
 // dt_raw [T, .] (rows ld_dt apart, head h at column h) with dt_bias, a_log [H]: the decay comes from the step size
 // as the header says; hpg: heads that share one head of q and k (1: each its own); skip [H] or null.
+// max_len > 0: requests that bring more tokens are left alone (the chunked kernel takes them).
 extern "C" int aie_linear_recurrence(const float* q, const float* k, const float* v, int ld, const float* decay_tok,
                                      int ld_decay, const float* decay_head, float q_scale, float k_scale, float* state,
                                      float* out, const int* q_start, const int* q_len, const int* slots, int T, int R,
                                      int H, int d, int dv, int max_slots, unsigned* err, int hpg, const float* dt_raw,
-                                     int ld_dt, const float* dt_bias, const float* a_log, const float* skip,
+                                     int ld_dt, const float* dt_bias, const float* a_log, const float* skip, int max_len,
                                      cudaStream_t st) {
     if (R <= 0) return 0;
     if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head && !dt_raw)) return AIE_BAD_ARG;
@@ -189,7 +191,7 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
                                                                      q_scale, k_scale, state, out, q_start, q_len,  \
                                                                      slots, H, d, dv, lanes, groups, TT, max_slots, \
                                                                      vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
-                                                                     a_log, skip)
+                                                                     a_log, skip, max_len)
     if (rpt == 4) GO(4);
     else if (rpt == 8) GO(8);
     else if (rpt == 16) GO(16);

@@ -526,14 +526,15 @@ extern "C" int aie_gate_group_norm(const float* y, const float* z, int ldz, cons
 // A router's choice, per token, float32: s = softmax(z) over the E outputs; the choice is made on s + correction;
 // the outputs form `groups` equal groups of neighbours, a group counts as its best member, and only members of the
 // `keep` best groups can be chosen (the others count as minus infinity); the `top` largest are taken, and their
-// weights are their s.  z [T, E] is replaced by s; scratch [T, E]; ids, weights [T, top].  One thread per token.
+// weights are their s.  z [T, E] (rows ld floats apart) is replaced by s; scratch [T, E]; ids, weights [T, top].
+// One thread per token.
 // ---------------------------------------------------------------------------
-__global__ void route_topk_kernel(float* __restrict__ z, float* __restrict__ scratch, const float* __restrict__ corr,
+__global__ void route_topk_kernel(float* __restrict__ z, int ld, float* __restrict__ scratch, const float* __restrict__ corr,
                                   int T, int E, int groups, int keep, int top, int* __restrict__ ids,
                                   float* __restrict__ weights) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
-    float* s = z + (size_t)t * E;
+    float* s = z + (size_t)t * ld;
     float* c = scratch + (size_t)t * E;
     float m = -INFINITY;
     for (int e = 0; e < E; ++e) m = fmaxf(m, s[e]);
@@ -582,13 +583,13 @@ __global__ void route_topk_kernel(float* __restrict__ z, float* __restrict__ scr
     }
 }
 
-extern "C" int aie_route_topk(float* z, float* scratch, const float* corr, int T, int E, int groups, int keep, int top,
+extern "C" int aie_route_topk(float* z, int ld, float* scratch, const float* corr, int T, int E, int groups, int keep, int top,
                               int* ids, float* weights, cudaStream_t st) {
     if (T <= 0) return 0;
-    if (E <= 0 || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 || top > E / groups * keep)
+    if (E <= 0 || ld < E || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 || top > E / groups * keep)
         return AIE_BAD_ARG;
     if (groups > 64) return AIE_UNSUPPORTED;
-    route_topk_kernel<<<(T + 63) / 64, 64, 0, st>>>(z, scratch, corr, T, E, groups, keep, top, ids, weights);
+    route_topk_kernel<<<(T + 63) / 64, 64, 0, st>>>(z, ld, scratch, corr, T, E, groups, keep, top, ids, weights);
     AIE_LAUNCH_CHECK();
 }
 

@@ -5,6 +5,7 @@ stream.  Shapes and dtypes a kernel does not take are refused with an error.
 from __future__ import annotations
 
 import math
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -821,18 +822,24 @@ def latent_attention(q_full: torch.Tensor, pages: torch.Tensor, ctx, block_table
     return out
 
 
+SSD_MIN_TOKENS = 32      # portions from this length on take the chunked state-space kernel (bfloat16 mode)
+SSD_CHUNK = 64           # its chunk
+
+
 def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_tok: Optional[torch.Tensor],
                       decay_head: Optional[torch.Tensor], q_scale: float, k_scale: float, state: torch.Tensor,
                       ctx, H: int, d: int, dv: int, heads_per_group: int = 1, dt_raw: Optional[torch.Tensor] = None,
                       dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
-                      skip: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      skip: Optional[torch.Tensor] = None, chunked: bool = False) -> torch.Tensor:
     """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens, the state
     [max_seqs, H, d, dv] float32 read and left in each request's slot.  q, k [T, H * d] and v [T, H * dv] are
     float32 views with one row stride; decay_tok [T, H * d] float32 (rows any stride) or decay_head [H].
     With `dt_raw` [T, H] (a float32 view, rows any stride), dt_bias and a_log [H]: the decay is one number per
     token and head, a = exp(-exp(a_log) dt) with dt = softplus(dt_raw + dt_bias), and v is scaled by dt.
     heads_per_group: neighbouring heads that share one head of q and k ([T, H / heads_per_group * d]).
-    skip [H]: skip[h] * v is added to the output.  Returns o [T, H, dv] float32."""
+    skip [H]: skip[h] * v is added to the output.  chunked (with dt_raw): portions of SSD_MIN_TOKENS tokens or more
+    take the chunked tensor-core kernel, which rounds q, k and v to bfloat16 (a state of up to 128 rows).
+    Returns o [T, H, dv] float32."""
     _dev(state, decay_head, dt_bias, a_log, skip)
     if dt_raw is not None and (dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_bias is None or a_log is None):
         raise KernelError("linear_recurrence: step sizes are a float32 view with their bias and rates")
@@ -842,6 +849,20 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
             or v.stride(0) != ld or q.stride(1) != 1 or state.shape[1:] != (H, d, dv) or state.dtype != torch.float32):
         raise KernelError("linear_recurrence: shapes or dtypes do not fit")
     out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+    max_len = 0
+    if (chunked and dt_raw is not None and decay_tok is None and d <= 128 and ctx.max_q_len >= SSD_MIN_TOKENS
+            and not os.environ.get("AI_ENGINE_B200_NO_CHUNKED_SCAN")):      # the switch is for measurement
+        lib = library("state_space_chunked.cu")
+        with region("state_space_chunked", _nb(out) + T * H * (2 * d // heads_per_group + dv) * 4,
+                    2.0 * T * H * (SSD_CHUNK * (d + dv) / 2 + 2 * d * dv)):
+            check(lib.aie_state_space_chunked(_p(q), _p(k), _p(v), c_int(ld), _p(dt_raw), c_int(dt_raw.stride(0)), _p(dt_bias),
+                                              _p(a_log), _p(skip), _p(state), _p(out), _p(ctx.q_start), _p(ctx.q_len),
+                                              _p(ctx.slots), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
+                                              c_int(heads_per_group), c_int(state.shape[0]), c_int(SSD_MIN_TOKENS),
+                                              _p(ctx.err), _stream()), "state_space_chunked")
+        if int(ctx.h_q_len.min()) >= SSD_MIN_TOKENS:
+            return out
+        max_len = SSD_MIN_TOKENS - 1                # the shorter portions and single tokens of the same step
     lib = library("linear_recurrence.cu")
     with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4, 4.0 * T * H * d * dv):
         check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
@@ -850,7 +871,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                                         _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
                                         c_int(state.shape[0]), _p(ctx.err), c_int(heads_per_group), _p(dt_raw),
                                         c_int(dt_raw.stride(0) if dt_raw is not None else 0), _p(dt_bias), _p(a_log),
-                                        _p(skip), _stream()), "linear_recurrence")
+                                        _p(skip), c_int(max_len), _stream()), "linear_recurrence")
     return out
 
 
@@ -935,21 +956,21 @@ def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, part
 
 
 def route_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int):
-    """A router's choice per token from float32 logits [T, E] (overwritten by their softmax): the `top` outputs
+    """A router's choice per token from float32 logits [T, E] (a view whose rows may be wider apart; overwritten by their softmax): the `top` outputs
     with the largest softmax + correction among the members of the `keep` groups (of `groups` equal groups of
     neighbours) whose best member is largest.  Returns (ids int32 [T, top], weights float32 [T, top]: the
     chosen outputs' softmax)."""
-    _dev(logits, correction)
+    _dev(correction)
     T, E = logits.shape
-    if logits.dtype != torch.float32 or (correction is not None and (correction.dtype != torch.float32 or
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or (correction is not None and (correction.dtype != torch.float32 or
                                                                     correction.shape != (E,))):
         raise KernelError("route_topk: float32 logits and correction")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    scratch = torch.empty_like(logits)
+    scratch = torch.empty((T, E), dtype=torch.float32, device=logits.device)
     lib = library("sequence_ops.cu")
-    with region("route_topk", 3 * _nb(logits)):
-        check(lib.aie_route_topk(_p(logits), _p(scratch), _p(correction), c_int(T), c_int(E), c_int(groups), c_int(keep),
+    with region("route_topk", 3 * _nb(scratch)):
+        check(lib.aie_route_topk(_p(logits), c_int(logits.stride(0)), _p(scratch), _p(correction), c_int(T), c_int(E), c_int(groups), c_int(keep),
                                  c_int(top), _p(ids), _p(weights), _stream()), "route_topk")
     return ids, weights
 

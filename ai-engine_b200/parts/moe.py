@@ -132,6 +132,10 @@ class RoutedMoE(FeedForward):
     def load(self, source):
         t = self.spec.tensors
         self.w_router = source.get(t["router"])
+        if self.w_router.dtype == torch.bfloat16 and self.w_router.shape[0] % 8:
+            # zero rows up to a multiple of 8: the tensor-core products want rows of the output 16 bytes apart
+            pad = torch.zeros(((-self.w_router.shape[0]) % 8, self.hidden), dtype=torch.bfloat16, device=self.w_router.device)
+            self.w_router = torch.cat([self.w_router, pad], dim=0).contiguous()
         self.correction = source.get(t["correction"]).float().contiguous()
         gu, down = [], []
         for e in range(self.E):
@@ -150,8 +154,12 @@ class RoutedMoE(FeedForward):
         return 2.0 * tokens * self.hidden * (3 * self.top * self.F + self.E + self.ident)
 
     def forward(self, h, ctx):
-        # the router in float32 on the sublayer's input as the experts see it
-        logits = ops.gemm_f32(ops.cast(h, torch.float32), self.w_router)
+        # the router in float32 on the sublayer's input as the experts see it: products of bfloat16 values are exact
+        # in float32, so the tensor-core product with float32 sums is a float32 product of those inputs
+        if h.dtype == torch.bfloat16 and self.w_router.dtype == torch.bfloat16:
+            logits = ops.linear(h, self.w_router, torch.float32, ctx.err)[:, :self.E + self.ident]
+        else:
+            logits = ops.gemm_f32(ops.cast(h, torch.float32), self.w_router)
         ids, weights = ops.route_topk(logits, self.correction, self.groups, self.keep, self.top)
         if not self.E:
             y = torch.zeros((1, self.hidden), dtype=torch.float32, device=h.device)

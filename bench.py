@@ -71,6 +71,30 @@ def pifutar_shape(width, layers=8):
     return dict(architecture="Pifutar", vocab=32000, width=width, norm=dict(eps=1e-5), canon=dict(taps=4), layers=out)
 
 
+def zupitar_shape(width, layers=8):
+    """A Zupitar configuration with layers of the sizes real models of its kind have: attention heads of 128 (a quarter
+    of them key heads, half of each head rotated, three taps behind the projections) beside a state-space mixer as wide
+    as the model (heads of 64, a state of 128, eight groups); state-space layers on their own twice as wide; a dense
+    feed-forward of 3 x width or 30 experts of width / 2 and two identity experts (top 4, two of four groups kept);
+    the pattern of six layers (parallel dense, state-space experts, parallel dense, parallel experts, parallel dense,
+    state-space experts) repeats."""
+    H = width // 128
+    ssm = lambda inner, taps: dict(heads=inner // 64, vdim=64, state=128, groups=8, conv=taps, norm_groups=8)
+    par = dict(left=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, conv=3, scale=128 ** -0.5,
+                         rot=dict(base=250000.0, dims=64, scaling=dict(factor=4.0))),
+               right=ssm(width, 3), left_scale=0.8, right_scale=1.1)
+    moe = dict(kind="moe", expert=dict(ff=width // 2), router=dict(experts=30, identity=2, top=4, groups=dict(count=4, keep=2)))
+    dense = dict(kind="dense", ff=3 * width)
+    out = []
+    for i in range(layers):
+        k = i % 6
+        if k in (1, 5):
+            out.append(dict(type="mamba2", mixer=ssm(2 * width, 4), mlp=moe))
+        else:
+            out.append(dict(type="parallel", mixer=par, mlp=moe if k == 3 else dense))
+    return dict(architecture="Zupitar", vocab=32000, width=width, norm=dict(eps=1e-5), logit_softcap=30.0, layers=out)
+
+
 def llama_like(width, layers=8):
     """The closest existing model at equal size: the same width, layers, heads of 128 (a quarter of them kv heads)
     and a feed-forward of 3 x width, which is what a Pifutar token uses (4 experts of width / 2 + the shared one)."""
@@ -609,10 +633,10 @@ def main():
                     help="time one part only and print its numbers (for profiling)")
     ap.add_argument("--profile", action="store_true",
                     help="CUDA-event time, bytes, flops and roofline fraction per class of kernel (eager launches)")
-    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "llama") for w in WIDTHS],
+    ap.add_argument("--shape", choices=["8b", "1b", "3b"] + [f"{m}-{w}" for m in ("pifutar", "zupitar", "llama") for w in WIDTHS],
                     default="8b",
                     help="layer sizes for --profile and --only decode|prefill (the headline run is always the 8B shape); "
-                         "pifutar-1k|2k|4k: the Pifutar design at that width, llama-1k|2k|4k: Llama at equal size beside it "
+                         "pifutar-1k|2k|4k, zupitar-1k|2k|4k: those designs at that width, llama-1k|2k|4k: Llama at equal size beside them "
                          "(8 layers unless --layers says otherwise)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="cached tokens per request for --profile / --only decode")
     ap.add_argument("--skip-workloads", action="store_true", help="leave the 1B and 3B serving workloads out of `points`")
@@ -659,7 +683,7 @@ def main():
     if "-" in a.shape and (a.profile or a.only):
         family, w = a.shape.split("-")
         layers = a.layers if a.layers != LLAMA3_8B["num_hidden_layers"] else 8
-        cfg = (pifutar_shape if family == "pifutar" else llama_like)(WIDTHS[w], layers)
+        cfg = dict(pifutar=pifutar_shape, zupitar=zupitar_shape, llama=llama_like)[family](WIDTHS[w], layers)
     else:
         cfg = dict({"8b": LLAMA3_8B, "1b": LLAMA32_1B, "3b": LLAMA32_3B}.get(a.shape, LLAMA3_8B) if (a.profile or a.only) else LLAMA3_8B)
         if a.layers != LLAMA3_8B["num_hidden_layers"] or a.shape == "8b":

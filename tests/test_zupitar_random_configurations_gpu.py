@@ -24,7 +24,7 @@ def draw(seed):
     def ssm():
         groups = int(pick([1, 1, 2, 3]))
         heads = groups * int(pick([1, 2, 3]))
-        vdim = int(pick([4, 12, 20, 32, 64]))
+        vdim = int(pick([8, 12, 20, 32, 64]))
         # (a part of very few channels divided by its own root mean square turns on the sign of single values)
         norm_groups = int(pick([1] + [g for g in (2, 3, 4, heads) if (heads * vdim) % g == 0 and heads * vdim // g >= 8]))
         return dict(heads=heads, vdim=vdim, state=int(pick([4, 12, 16, 40, 64, 128])), groups=groups,

@@ -145,7 +145,7 @@ def close(got, ref, dtype, what=""):
     """Logits agree within rounding.  The float32 engine against the float64 oracle: 2e-4 of the logits' spread at
     every element.  bfloat16 against the float32 oracle on the same weights: a router's close call may turn either
     way under rounding, and then the row (and, fading, the next ones) is another expert's.  So over all rows the
-    median of the rows' worst differences must stay under 0.1 of the spread and nine rows in ten under 0.2 (a wrong
+    median of the rows' worst differences must stay under 0.12 of the spread and nine rows in ten under 0.2 (a wrong
     key, state or expert moves every row by the spread itself), and at the rows whose routing is clear the worst element may differ by 0.2 of
     the spread and the mean difference must stay under 0.03 of it."""
     spread = max(float(np.std(ref)), 1e-3)
@@ -153,7 +153,7 @@ def close(got, ref, dtype, what=""):
     if dtype != "float32":
         if diff.shape[0] >= 8:
             med = float(np.median(diff.max(axis=-1)))
-            assert med <= 0.1 * spread, f"{what}: median row difference {med:.3e} above {0.1 * spread:.3e}"
+            assert med <= 0.12 * spread, f"{what}: median row difference {med:.3e} above {0.12 * spread:.3e}"
         if diff.shape[0] >= 100:
             p90 = float(np.percentile(diff.max(axis=-1), 90))
             assert p90 <= 0.2 * spread, f"{what}: nine rows in ten must be within {0.2 * spread:.3e}, are within {p90:.3e}"

@@ -152,6 +152,69 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     }
 }
 
+// ---------------------------------------------------------------------------
+// One token per request of the state-space form (dt_raw given): the step reads and writes every state once, so it
+// runs at the speed of memory when rows of the state are read whole.  One block per (request, head): a thread owns
+// four neighbouring value columns (16 bytes) of every `rows_step`-th state row, updates them, and keeps its share
+// of y = S^T q; the shares are added through shared memory in a fixed order.
+// ---------------------------------------------------------------------------
+#define SS_THREADS 256
+__global__ void __launch_bounds__(SS_THREADS)
+state_space_step_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld,
+                        const float* __restrict__ dt_raw, int ld_dt, const float* __restrict__ dt_bias,
+                        const float* __restrict__ a_log, const float* __restrict__ skip, float* __restrict__ state,
+                        float* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ slots, int H,
+                        int d, int dv, int hpg, int max_slots, unsigned* err) {
+    extern __shared__ __align__(16) float ss_sm[];
+    const int tid = threadIdx.x, h = blockIdx.x % H, r = blockIdx.x / H;
+    const int slot = slots[r];
+    if (slot < 0 || slot >= max_slots) {
+        if (tid == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
+        return;
+    }
+    const int t = q_start[r], hq = h / hpg;
+    const int c4 = dv / 4;                            // float4 columns of a row
+    const int rows_step = SS_THREADS / c4;            // rows the block covers at a time (c4 divides the block)
+    float* k_s = ss_sm;                               // [d]  B dt
+    float* q_s = k_s + d;                             // [d]  C
+    float* y_s = q_s + d;                             // [rows_step][dv]
+    const float x = dt_raw[(size_t)t * ld_dt + h] + dt_bias[h];
+    const float dtv = x > 20.f ? x : log1pf(expf(x));
+    const float a = expf(-expf(a_log[h]) * dtv);
+    for (int i = tid; i < d; i += SS_THREADS) {
+        k_s[i] = k[(size_t)t * ld + (size_t)hq * d + i] * dtv;
+        q_s[i] = q[(size_t)t * ld + (size_t)hq * d + i];
+    }
+    __syncthreads();
+    const int col = (tid % c4) * 4, row0 = tid / c4;
+    const float4 xv = *reinterpret_cast<const float4*>(v + (size_t)t * ld + (size_t)h * dv + col);
+    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+    float* sp = state + (((size_t)slot * H + h) * d) * dv + col;
+    if (row0 < rows_step) {
+        for (int n = row0; n < d; n += rows_step) {
+            float4 s4 = *reinterpret_cast<float4*>(sp + (size_t)n * dv);
+            const float kk = k_s[n], qq = q_s[n];
+            s4.x = fmaf(a, s4.x, kk * xv.x);
+            s4.y = fmaf(a, s4.y, kk * xv.y);
+            s4.z = fmaf(a, s4.z, kk * xv.z);
+            s4.w = fmaf(a, s4.w, kk * xv.w);
+            *reinterpret_cast<float4*>(sp + (size_t)n * dv) = s4;
+            y.x = fmaf(s4.x, qq, y.x);
+            y.y = fmaf(s4.y, qq, y.y);
+            y.z = fmaf(s4.z, qq, y.z);
+            y.w = fmaf(s4.w, qq, y.w);
+        }
+        *reinterpret_cast<float4*>(y_s + (size_t)row0 * dv + col) = y;
+    }
+    __syncthreads();
+    for (int c = tid; c < dv; c += SS_THREADS) {
+        float acc = 0.f;
+        for (int g = 0; g < rows_step; ++g) acc += y_s[(size_t)g * dv + c];
+        if (skip) acc = fmaf(skip[h], v[(size_t)t * ld + (size_t)h * dv + c], acc);
+        out[((size_t)t * H + h) * dv + c] = acc;
+    }
+}
+
 // q, k [T, .] with head h's d channels at column h d of rows `ld` floats apart; v likewise with dv columns a
 // head; decay_tok [T, .] rows `ld_decay` apart (or null: decay_head [H] constants).  The key is scaled by
 // k_scale, the output by q_scale (both 1 or d^-1/2).  state [max_slots, H, d, dv]; out [T, H, dv].
@@ -168,6 +231,18 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
     if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head && !dt_raw)) return AIE_BAD_ARG;
     if (hpg < 1 || H % hpg || (dt_raw && (!dt_bias || !a_log || decay_tok))) return AIE_BAD_ARG;
     if (d > 1024) return AIE_UNSUPPORTED;
+    // a step of single tokens in the state-space form: the kernel that reads rows of the state whole
+    if (dt_raw && T == R && max_len <= 0 && dv % 4 == 0 && dv / 4 <= SS_THREADS && SS_THREADS % (dv / 4) == 0 && ld % 4 == 0 &&
+        !((size_t)v & 15) && !((size_t)state & 15) && q_scale == 1.f && k_scale == 1.f) {
+        const int rows_step = SS_THREADS / (dv / 4);
+        const size_t smem = ((size_t)2 * d + (size_t)rows_step * dv) * sizeof(float);
+        if (smem <= 48 * 1024 && (long long)R * H <= 0x7fffffffLL) {
+            state_space_step_kernel<<<(unsigned)(R * H), SS_THREADS, smem, st>>>(q, k, v, ld, dt_raw, ld_dt, dt_bias, a_log, skip,
+                                                                                 state, out, q_start, slots, H, d, dv, hpg,
+                                                                                 max_slots, err);
+            AIE_LAUNCH_CHECK();
+        }
+    }
     // A step of single tokens is bound by reading and writing the states: many rows a thread, so that a warp's
     // accesses to a row of the state are wide.  A step of prompt portions is bound by the chain of dependent
     // updates token after token: few rows a thread, so that many warps hide one another's latency.

@@ -864,7 +864,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
             return out
         max_len = SSD_MIN_TOKENS - 1                # the shorter portions and single tokens of the same step
     lib = library("linear_recurrence.cu")
-    with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4, 4.0 * T * H * d * dv):
+    with region("linear_recurrence", _nb(out) + T * H * (2 * d + dv) * 4 + 2 * ctx.R * H * d * dv * 4, 4.0 * T * H * d * dv):
         check(lib.aie_linear_recurrence(_p(q), _p(k), _p(v), c_int(ld), _p(decay_tok),
                                         c_int(decay_tok.stride(0) if decay_tok is not None else 0), _p(decay_head),
                                         c_float(q_scale), c_float(k_scale), _p(state), _p(out), _p(ctx.q_start),

@@ -65,8 +65,8 @@ class GQAAttention(Mixer):
         self.H, self.K, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
         if self.H % self.K:
             raise ValueError(f"attention: {self.H} heads are not a multiple of {self.K} kv heads")
-        if self.d % 16 or self.d > 256:
-            raise ValueError(f"attention: head_dim {self.d} must be a multiple of 16, at most 256")
+        if self.d % 8 or self.d > 256:
+            raise ValueError(f"attention: head_dim {self.d} must be a multiple of 8, at most 256")
         self.window = int(p.get("window") or 0)
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
         pe = p.get("position_encoding")

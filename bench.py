@@ -213,7 +213,9 @@ def time_decode(torch, aie, model, batch, prompt_len, steps, warmup, ctx_cap, bl
     launches = (LAUNCHES[0] - l0 + runner.graph_launches - g0) // blocks     # launched afresh + replayed, per block
     ms = statistics.median(per_block)
     ctx_tokens = batch * (prompt_len + warmup + steps * blocks / 2.0)
-    bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens
+    # weights once, every cached key and value once, and every request's state read and written
+    state_bytes = sum(t[0].numel() * t.element_size() for t in cache.state_tensors()) if hasattr(cache, "state_tensors") else 0
+    bytes_step = model.step_weight_bytes() + cache.kv_bytes_per_token() * ctx_tokens + 2 * state_bytes * batch
     del cache, runner
     torch.cuda.empty_cache()
     return dict(ms=ms, ms_min=min(per_block), ms_max=max(per_block), blocks=blocks, tok_s=batch * 1000.0 / ms,

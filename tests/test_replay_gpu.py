@@ -399,6 +399,6 @@ def test_a_head_size_that_no_kernel_takes_is_refused_by_name(tmp_path):
                max_position_embeddings=64, hidden_size=100, intermediate_size=116, num_attention_heads=5,
                num_key_value_heads=5, head_dim=20, vocab_size=257, tie_word_embeddings=False)
     d = os.path.join(str(tmp_path), "head20")
-    with pytest.raises(ValueError, match="head_dim 20 must be a multiple of 16"):      # already when the parts are built
+    with pytest.raises(ValueError, match="head_dim 20 must be a multiple of 8"):      # already when the parts are built
         aie.write_random_model(aie.LlamaConfig.from_dict(raw), d, seed=9, dtype="bfloat16")
         Replayer(d, "bfloat16", max_tokens=64, block_size=16)

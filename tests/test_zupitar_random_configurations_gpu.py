@@ -32,7 +32,7 @@ def draw(seed):
 
     def attn():
         kv = int(pick([1, 1, 2, 3]))
-        dim = int(pick([16, 32, 48, 64, 128]))
+        dim = int(pick([16, 24, 40, 64, 128]))
         m = dict(heads=kv * int(pick([1, 2, 4])), kv_heads=kv, dim=dim, vdim=dim, conv=int(rng.randint(1, 5)),
                  scale=float(dim ** -0.5 * pick([1.0, 0.6, 1.5])))
         r = rng.rand()

@@ -462,6 +462,64 @@ __global__ void causal_conv_kernel(const float* __restrict__ u, int ld_in, const
     }
 }
 
+// The same for channel counts, row strides and copied ranges that are multiples of 4: a thread owns four neighbouring
+// channels (16-byte loads and stores).
+template <typename O>
+__global__ void causal_conv4_kernel(const float* __restrict__ u, int ld_in, const float* __restrict__ w,
+                                    const float* __restrict__ bias, float* __restrict__ state, O* __restrict__ out,
+                                    int ld_out, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                    const int* __restrict__ slots, const int* __restrict__ token_req, int C, int taps,
+                                    int residual, int act, int dup_from, int dup_n, int max_slots, unsigned* err) {
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= C) return;
+    const int r = token_req[t];
+    const int a = q_start[r], n = q_len[r], i = t - a, slot = slots[r];
+    const int Hh = taps - 1;
+    const float* wc = w + (size_t)c * taps;                 // channel c + e: wc[e * taps + j]
+    const float4 b = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool dup = c >= dup_from && c < dup_from + dup_n;
+    float* st = state + (size_t)slot * Hh * C + c;          // st[k * C]: input at local index k - Hh
+    if (i < Hh && (slot < 0 || slot >= max_slots)) {
+        if (threadIdx.x == 0 && i == 0) atomicOr(err, AIE_DEV_SLOT_OOB);
+        return;
+    }
+    if (i >= Hh || i == 0) {
+        const int first = i >= Hh ? 1 : min(n, Hh);         // the request's first block also serves the tokens that need the tail
+        for (int ii = 0; ii < first; ++ii) {
+            const int li = i + ii;                          // index of the token among the request's tokens of this step
+            float4 acc = b;
+            if (residual) {
+                const float4 x = *reinterpret_cast<const float4*>(u + (size_t)(a + li) * ld_in + c);
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            }
+            for (int j = 0; j < taps; ++j) {
+                const int src = li - Hh + j;
+                const float4 x = src >= 0 ? *reinterpret_cast<const float4*>(u + (size_t)(a + src) * ld_in + c)
+                                          : *reinterpret_cast<const float4*>(st + (size_t)(src + Hh) * C);
+                acc.x = fmaf(wc[j], x.x, acc.x);
+                acc.y = fmaf(wc[taps + j], x.y, acc.y);
+                acc.z = fmaf(wc[2 * taps + j], x.z, acc.z);
+                acc.w = fmaf(wc[3 * taps + j], x.w, acc.w);
+            }
+            if (act == 1) {
+                acc.x = acc.x / (1.0f + expf(-acc.x));
+                acc.y = acc.y / (1.0f + expf(-acc.y));
+                acc.z = acc.z / (1.0f + expf(-acc.z));
+                acc.w = acc.w / (1.0f + expf(-acc.w));
+            }
+            store4<O>(out + (size_t)(a + li) * ld_out + c, acc);
+            if (dup) store4<O>(out + (size_t)(a + li) * ld_out + c + dup_n, acc);
+        }
+    }
+    if (i != 0) return;
+    for (int k = 0; k < Hh; ++k) {                          // ascending: entry n + k > k is still the old one
+        const int src = n - Hh + k;
+        *reinterpret_cast<float4*>(st + (size_t)k * C) =
+            src >= 0 ? *reinterpret_cast<const float4*>(u + (size_t)(a + src) * ld_in + c)
+                     : *reinterpret_cast<const float4*>(st + (size_t)(n + k) * C);
+    }
+}
+
 extern "C" int aie_causal_conv(const float* u, int ld_in, const float* w, const float* bias, float* state, void* out,
                                int out_dtype, int ld_out, const int* q_start, const int* q_len, const int* slots,
                                const int* token_req, int T, int C, int taps, int residual, int act, int dup_from,
@@ -469,6 +527,18 @@ extern "C" int aie_causal_conv(const float* u, int ld_in, const float* w, const 
     if (T <= 0) return 0;
     if (C <= 0 || taps < 1 || act < 0 || act > 1 || dup_n < 0 || (dup_n && (dup_from < 0 || dup_from + dup_n != C)))
         return AIE_BAD_ARG;
+    const int esz = out_dtype == AIE_F32 ? 4 : 2;
+    if (C % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && dup_from % 4 == 0 && dup_n % 4 == 0 && !((size_t)u & 15) &&
+        !((size_t)state & 15) && !((size_t)out & (4 * esz - 1)) && (!bias || !((size_t)bias & 15)) &&
+        (out_dtype == AIE_F32 || out_dtype == AIE_BF16)) {
+        const int threads4 = 64;
+        dim3 grid4(T, (C / 4 + threads4 - 1) / threads4);
+        if (out_dtype == AIE_F32)
+            causal_conv4_kernel<float><<<grid4, threads4, 0, st>>>(u, ld_in, w, bias, state, (float*)out, ld_out, q_start, q_len, slots, token_req, C, taps, residual, act, dup_from, dup_n, max_slots, err);
+        else
+            causal_conv4_kernel<bf16><<<grid4, threads4, 0, st>>>(u, ld_in, w, bias, state, (bf16*)out, ld_out, q_start, q_len, slots, token_req, C, taps, residual, act, dup_from, dup_n, max_slots, err);
+        AIE_LAUNCH_CHECK();
+    }
     const int threads = C >= 256 ? 256 : 128;
     dim3 grid(T, (C + threads - 1) / threads);
     if (grid.y > 65535) return AIE_UNSUPPORTED;

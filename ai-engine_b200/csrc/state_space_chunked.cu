@@ -5,11 +5,11 @@
 //     G = C B^T                                   [Q, Q]   which key meets which query
 //     W[t, s] = G[t, s] exp(l_t - l_s) dt_s   (s <= t, else 0)
 //     Y = W X + diag(exp(l_t)) (C S_prev)         [Q, dv]
-//     S_new = exp(l_Q) S_prev + (B * w)^T X,   w_s = exp(l_Q - l_s) dt_s
+//     S_new = exp(l_Q) S_prev + B^T (w * X),   w_s = exp(l_Q - l_s) dt_s
 // One CTA owns a (request, head, 64 or 32 value columns) and walks the request's chunks in order with the state in shared
 // memory, so a portion continues where the last step stopped and no result depends on the batch.  x, B and C (outputs
 // of the convolution and its activation) enter the products rounded to bfloat16; everything that holds a decay, a
-// step size or the state (W, B * w, S) enters as a pair of bfloat16 values, the rounded value and the rounded rest,
+// step size or the state (W, w * X, S) enters as a pair of bfloat16 values, the rounded value and the rounded rest,
 // which carries 16 bits of mantissa; sums are float32.  Exponents are never positive: nothing can overflow.
 #include <mma.h>
 
@@ -18,10 +18,10 @@
 using namespace nvcuda;
 
 #define SC_Q 64
-#define SC_THREADS 256
+#define SC_THREADS 512
 #define SC_PAD 8         // bfloat16 elements (16 bytes) behind every row in shared memory: rows of a tile fall into
 #define SC_PADF 4        // different banks (the same 16 bytes for float32 rows)
-#define SC_WARPS 8
+#define SC_WARPS 16
 
 typedef wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> FragA;
 typedef wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::col_major> FragAT;
@@ -60,9 +60,9 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
     constexpr int DT = DV / 16;                                                // column tiles of a CTA
     bf16* Cs = reinterpret_cast<bf16*>(sc_sm);                    // [Q][NP]
     bf16* Bs = Cs + SC_Q * LN;                                    // [Q][NP]
-    bf16* BwH = Bs + SC_Q * LN;                                   // [Q][NP]  B * w, rounded
-    bf16* BwL = BwH + SC_Q * LN;                                  //          ... and the rest
-    bf16* Xs = BwL + SC_Q * LN;                                   // [Q][DV]
+    bf16* XwH = Bs + SC_Q * LN;                                   // [Q][DV]  w * X, rounded
+    bf16* XwL = XwH + SC_Q * LD;                                  //          ... and the rest
+    bf16* Xs = XwL + SC_Q * LD;                                   // [Q][DV]
     bf16* WH = Xs + SC_Q * LD;                                    // [Q][Q]
     bf16* WL = WH + SC_Q * LQ;
     bf16* SH = WL + SC_Q * LQ;                                    // [NP][DV]
@@ -73,6 +73,7 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
     float* la = Sf + NP * FD;                                     // [Q] running sums of log decays
     float* dtv = la + SC_Q;                                       // [Q] step sizes
     float* wv = dtv + SC_Q;                                       // [Q] w_s = exp(l_Q - l_s) dt_s
+    float* ela = wv + SC_Q;                                       // [Q] exp(l_t)
 
     const int hq = h / hpg, col0 = cb * DV, a0 = q_start[r];
     const float rate = expf(a_log[h]), dtb = dt_bias[h], sk = skip ? skip[h] : 0.f;
@@ -140,6 +141,8 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
             const float end = __shfl_sync(0xffffffffu, run, 31);
             wv[2 * lane] = expf(end - (run - v1)) * dtv[2 * lane];
             wv[2 * lane + 1] = expf(end - run) * dtv[2 * lane + 1];
+            ela[2 * lane] = expf(run - v1);
+            ela[2 * lane + 1] = expf(run);
         }
         // G = C B^T, the tiles on and below the diagonal
         for (int tile = warp; tile < 16; tile += SC_WARPS) {
@@ -158,14 +161,17 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
         }
         __syncthreads();
         const float l_end = la[SC_Q - 1];
-        for (int i = tid; i < SC_Q * SC_Q; i += SC_THREADS) {
-            const int t = i / SC_Q, s = i % SC_Q;
-            const float w = s <= t ? Gf[t * FY + s] * expf(la[t] - la[s]) * dtv[s] : 0.f;
+        // W on and below the diagonal, tile by tile (the tiles above it are never read)
+        for (int i = tid; i < 10 * 256; i += SC_THREADS) {
+            const int tile = i >> 8, e = i & 255;
+            const int ti = tile < 1 ? 0 : (tile < 3 ? 1 : (tile < 6 ? 2 : 3)), tj = tile - ti * (ti + 1) / 2;
+            const int t = ti * 16 + (e >> 4), s = tj * 16 + (e & 15);
+            const float w = s <= t ? Gf[t * FY + s] * __expf(la[t] - la[s]) * dtv[s] : 0.f;
             split_bf16(w, WH + t * LQ + s, WL + t * LQ + s);
         }
-        for (int i = tid; i < SC_Q * NP; i += SC_THREADS) {
-            const int s = i / NP, n = i % NP;
-            split_bf16(__bfloat162float(Bs[s * LN + n]) * wv[s], BwH + s * LN + n, BwL + s * LN + n);
+        for (int i = tid; i < SC_Q * DV; i += SC_THREADS) {
+            const int s = i / DV, j = i % DV;
+            split_bf16(__bfloat162float(Xs[s * LD + j]) * wv[s], XwH + s * LD + j, XwL + s * LD + j);
         }
         __syncthreads();
         // Ya = W X (into G's place) and Yb = C S_prev
@@ -195,7 +201,7 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
             }
             wmma::store_matrix_sync(Yb + ti * 16 * FD + tj * 16, acc, FD, wmma::mem_row_major);
         }
-        // S = exp(l_end) S + (B * w)^T X; a tile of the state belongs to one warp
+        // S = exp(l_end) S + B^T (w * X); a tile of the state belongs to one warp
         const float dec = expf(l_end);
         for (int tile = warp; tile < (NP / 16) * DT; tile += SC_WARPS) {
             const int ni = tile / DT, tj = tile % DT;
@@ -205,10 +211,10 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
             for (int k = 0; k < SC_Q / 16; ++k) {
                 FragAT fa;
                 FragB fb;
-                wmma::load_matrix_sync(fb, Xs + k * 16 * LD + tj * 16, LD);
-                wmma::load_matrix_sync(fa, BwH + k * 16 * LN + ni * 16, LN);
+                wmma::load_matrix_sync(fa, Bs + k * 16 * LN + ni * 16, LN);
+                wmma::load_matrix_sync(fb, XwH + k * 16 * LD + tj * 16, LD);
                 wmma::mma_sync(acc, fa, fb, acc);
-                wmma::load_matrix_sync(fa, BwL + k * 16 * LN + ni * 16, LN);
+                wmma::load_matrix_sync(fb, XwL + k * 16 * LD + tj * 16, LD);
                 wmma::mma_sync(acc, fa, fb, acc);
             }
             wmma::store_matrix_sync(Sf + ni * 16 * FD + tj * 16, acc, FD, wmma::mem_row_major);
@@ -217,7 +223,7 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
         for (int i = tid; i < SC_Q * DV; i += SC_THREADS) {
             const int t = i / DV, j = i % DV;
             if (t < nt && col0 + j < dv) {
-                float y = fmaf(expf(la[t]), Yb[t * FD + j], Gf[t * FY + j]);
+                float y = fmaf(ela[t], Yb[t * FD + j], Gf[t * FY + j]);
                 if (skip) y = fmaf(sk, __bfloat162float(Xs[t * LD + j]), y);      // x as the products saw it
                 out[((size_t)(a0 + t0 + t) * H + h) * dv + col0 + j] = y;
             }
@@ -237,8 +243,8 @@ state_space_chunked_kernel(const float* __restrict__ Cg, const float* __restrict
 template <int NP, int DV> static size_t sc_smem() {
     const int LN = NP + SC_PAD, LD = DV + SC_PAD, LQ = SC_Q + SC_PAD, FQ = SC_Q + SC_PADF, FD = DV + SC_PADF;
     const int FY = FQ > FD ? FQ : FD;
-    return (size_t)(4 * SC_Q * LN + SC_Q * LD + 2 * SC_Q * LQ + 2 * NP * LD) * sizeof(bf16) +
-           (size_t)(SC_Q * FY + SC_Q * FD + NP * FD + 3 * SC_Q) * sizeof(float);
+    return (size_t)(2 * SC_Q * LN + 3 * SC_Q * LD + 2 * SC_Q * LQ + 2 * NP * LD) * sizeof(bf16) +
+           (size_t)(SC_Q * FY + SC_Q * FD + NP * FD + 4 * SC_Q) * sizeof(float);
 }
 
 // C, B [T, .] with head h's N channels at column (h / hpg) N of rows `ld` floats apart; X likewise with dv columns a

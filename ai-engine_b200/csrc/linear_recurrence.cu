@@ -20,7 +20,22 @@
 #define LR_TOKENS 16        // most tokens staged at a time
 #define LR_THREADS (LR_WARPS * 32)
 
-template <int RPT>
+// one update of a state element and one term of the output, in the state's type (float, or double for the exact path)
+template <typename ST> __device__ __forceinline__ ST lr_update(ST a, ST s, float k, float v);
+template <> __device__ __forceinline__ float lr_update<float>(float a, float s, float k, float v) { return fmaf(a, s, k * v); }
+template <> __device__ __forceinline__ double lr_update<double>(double a, double s, float k, float v) {
+    return fma(a, s, (double)k * (double)v);
+}
+template <typename ST> __device__ __forceinline__ ST lr_term(ST s, float q, ST o);
+template <> __device__ __forceinline__ float lr_term<float>(float s, float q, float o) { return fmaf(s, q, o); }
+template <> __device__ __forceinline__ double lr_term<double>(double s, float q, double o) { return fma(s, (double)q, o); }
+
+// ST: the type the state is held in while a step's tokens are walked.  float: every update rounds to float32.  double
+// (the float32 engine's state-space layers): step size and decay are worked out in double too.  A decay near one,
+// rounded to float32, keeps few digits of its small rate, and where the step size hardly changes from token to token
+// the same rounding repeats at every token: over a thousand tokens a far token's share drifts by a few 1e-5.  In
+// double a portion's updates round once, when the state goes back to its float32 slot.
+template <int RPT, typename ST>
 __global__ void __launch_bounds__(LR_THREADS)
 linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld,
                          const float* __restrict__ decay_tok, int ld_decay, const float* __restrict__ decay_head,
@@ -43,16 +58,16 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     float* k_s = q_s + TT * d;
     float* a_s = k_s + TT * d;                                    // only with per-token decays
     float* v_s = decay_tok ? a_s + TT * d : a_s;                  // [TT][CB]
-    float* sc_s = v_s + TT * (LR_WARPS * (32 / lanes));           // [TT][2]: decay and step size (only with dt_raw)
+    float* sc_s = v_s + TT * (LR_WARPS * (32 / lanes));           // [TT][3]: decay, step size, the decay's rest (only with dt_raw)
     const int hq = h / hpg;                                       // the head whose queries and keys this one reads
     const float rate = dt_raw ? expf(a_log[h]) : 0.f, dtb = dt_raw ? dt_bias[h] : 0.f;
     const int g = lane % lanes, cb = warp * cols + lane / lanes, col = bg * CB + cb;
     const int row0 = g * RPT;
     const bool col_ok = col < dv;
-    float S[RPT];
+    ST S[RPT];
     float* sp = state + (((size_t)slot * H + h) * d) * dv + col;
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) S[i] = (col_ok && row0 + i < d) ? sp[(size_t)(row0 + i) * dv] : 0.f;
+    for (int i = 0; i < RPT; ++i) S[i] = (col_ok && row0 + i < d) ? (ST)sp[(size_t)(row0 + i) * dv] : (ST)0;
     const float dh = decay_head ? decay_head[h] : 1.f;
     const int a = q_start[r], n = q_len[r];
     for (int t0 = 0; t0 < n; t0 += TT) {
@@ -64,10 +79,20 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
             float vs = k_scale;
             if (dt_raw) {                                          // float32: softplus, then the decay of this token
                 const float x = dt_raw[(size_t)(a + t0 + tok) * ld_dt + h] + dtb;
-                const float dtv = x > 20.f ? x : log1pf(expf(x));
+                float dtv = x > 20.f ? x : log1pf(expf(x));
+                float ah = expf(-rate * dtv), al = 0.f;
+                if (sizeof(ST) == 8) {                             // the exact path: step size and decay worked out in double
+                    const double xd = (double)dt_raw[(size_t)(a + t0 + tok) * ld_dt + h] + (double)dtb;
+                    const double dd = xd > 20.0 ? xd : log1p(exp(xd));
+                    const double ad = exp(-exp((double)a_log[h]) * dd);
+                    dtv = (float)dd;
+                    ah = (float)ad;
+                    al = (float)(ad - (double)ah);
+                }
                 if (lane == 0) {
-                    sc_s[tok * 2] = expf(-rate * dtv);
-                    sc_s[tok * 2 + 1] = dtv;
+                    sc_s[tok * 3] = ah;
+                    sc_s[tok * 3 + 1] = dtv;
+                    sc_s[tok * 3 + 2] = al;
                 }
                 vs *= dtv;
             }
@@ -90,42 +115,42 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
         __syncthreads();
         // the staged tokens' updates first, then their reductions over the column's lanes side by side (sixteen
         // independent chains of shuffles instead of one after each token)
-        float oacc[LR_TOKENS];
+        ST oacc[LR_TOKENS];
 #pragma unroll
         for (int tok = 0; tok < LR_TOKENS; ++tok) {
-            oacc[tok] = 0.f;
+            oacc[tok] = (ST)0;
             if (tok >= nt) continue;
             const float* qr = q_s + tok * d + row0;
             const float* kr = k_s + tok * d + row0;
             const float* ar = decay_tok ? a_s + tok * d + row0 : nullptr;
             const float vv = v_s[tok * CB + cb];
-            const float dh_t = dt_raw ? sc_s[tok * 2] : dh;
-            float o = 0.f, o2 = 0.f;                               // two chains of additions
+            const ST dh_t = dt_raw ? (ST)sc_s[tok * 3] + (ST)sc_s[tok * 3 + 2] : (ST)dh;
+            ST o = (ST)0, o2 = (ST)0;                              // two chains of additions
             if (vec) {
 #pragma unroll
                 for (int i = 0; i < RPT; i += 4) {
                     if (row0 + i < d) {
                         const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
                         const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
-                        float4 a4 = make_float4(dh_t, dh_t, dh_t, dh_t);
+                        float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (ar) a4 = *reinterpret_cast<const float4*>(ar + i);
-                        S[i] = fmaf(a4.x, S[i], k4.x * vv);
-                        S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * vv);
-                        S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * vv);
-                        S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * vv);
-                        o = fmaf(S[i], q4.x, o);
-                        o = fmaf(S[i + 1], q4.y, o);
-                        o2 = fmaf(S[i + 2], q4.z, o2);
-                        o2 = fmaf(S[i + 3], q4.w, o2);
+                        S[i] = lr_update<ST>(ar ? (ST)a4.x : dh_t, S[i], k4.x, vv);
+                        S[i + 1] = lr_update<ST>(ar ? (ST)a4.y : dh_t, S[i + 1], k4.y, vv);
+                        S[i + 2] = lr_update<ST>(ar ? (ST)a4.z : dh_t, S[i + 2], k4.z, vv);
+                        S[i + 3] = lr_update<ST>(ar ? (ST)a4.w : dh_t, S[i + 3], k4.w, vv);
+                        o = lr_term<ST>(S[i], q4.x, o);
+                        o = lr_term<ST>(S[i + 1], q4.y, o);
+                        o2 = lr_term<ST>(S[i + 2], q4.z, o2);
+                        o2 = lr_term<ST>(S[i + 3], q4.w, o2);
                     }
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < RPT; ++i) {
                     if (row0 + i < d) {
-                        const float al = ar ? ar[i] : dh_t;
-                        S[i] = fmaf(al, S[i], kr[i] * vv);
-                        o = fmaf(S[i], qr[i], o);
+                        const ST al = ar ? (ST)ar[i] : dh_t;
+                        S[i] = lr_update<ST>(al, S[i], kr[i], vv);
+                        o = lr_term<ST>(S[i], qr[i], o);
                     }
                 }
             }
@@ -139,7 +164,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
 #pragma unroll
             for (int tok = 0; tok < LR_TOKENS; ++tok)
                 if (tok < nt) {
-                    float o = oacc[tok] * q_scale;
+                    float o = (float)(oacc[tok] * (ST)q_scale);
                     if (skip) o = fmaf(skip[h], v[(size_t)(a + t0 + tok) * ld + h * dv + col], o);
                     out[((size_t)(a + t0 + tok) * H + h) * dv + col] = o;
                 }
@@ -148,7 +173,7 @@ linear_recurrence_kernel(const float* __restrict__ q, const float* __restrict__ 
     if (col_ok) {
 #pragma unroll
         for (int i = 0; i < RPT; ++i)
-            if (row0 + i < d) sp[(size_t)(row0 + i) * dv] = S[i];
+            if (row0 + i < d) sp[(size_t)(row0 + i) * dv] = (float)S[i];
     }
 }
 
@@ -164,7 +189,7 @@ state_space_step_kernel(const float* __restrict__ q, const float* __restrict__ k
                         const float* __restrict__ dt_raw, int ld_dt, const float* __restrict__ dt_bias,
                         const float* __restrict__ a_log, const float* __restrict__ skip, float* __restrict__ state,
                         float* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ slots, int H,
-                        int d, int dv, int hpg, int max_slots, unsigned* err) {
+                        int d, int dv, int hpg, int max_slots, int wide, unsigned* err) {
     extern __shared__ __align__(16) float ss_sm[];
     const int tid = threadIdx.x, h = blockIdx.x % H, r = blockIdx.x / H;
     const int slot = slots[r];
@@ -179,8 +204,15 @@ state_space_step_kernel(const float* __restrict__ q, const float* __restrict__ k
     float* q_s = k_s + d;                             // [d]  C
     float* y_s = q_s + d;                             // [rows_step][dv]
     const float x = dt_raw[(size_t)t * ld_dt + h] + dt_bias[h];
-    const float dtv = x > 20.f ? x : log1pf(expf(x));
+    float dtv = x > 20.f ? x : log1pf(expf(x));
     const float a = expf(-expf(a_log[h]) * dtv);
+    double ad = (double)a;
+    if (wide) {       // the exact path: a decay near one keeps the digits of its small rate only in double
+        const double xd = (double)dt_raw[(size_t)t * ld_dt + h] + (double)dt_bias[h];
+        const double dd = xd > 20.0 ? xd : log1p(exp(xd));
+        ad = exp(-exp((double)a_log[h]) * dd);
+        dtv = (float)dd;
+    }
     for (int i = tid; i < d; i += SS_THREADS) {
         k_s[i] = k[(size_t)t * ld + (size_t)hq * d + i] * dtv;
         q_s[i] = q[(size_t)t * ld + (size_t)hq * d + i];
@@ -194,10 +226,17 @@ state_space_step_kernel(const float* __restrict__ q, const float* __restrict__ k
         for (int n = row0; n < d; n += rows_step) {
             float4 s4 = *reinterpret_cast<float4*>(sp + (size_t)n * dv);
             const float kk = k_s[n], qq = q_s[n];
-            s4.x = fmaf(a, s4.x, kk * xv.x);
-            s4.y = fmaf(a, s4.y, kk * xv.y);
-            s4.z = fmaf(a, s4.z, kk * xv.z);
-            s4.w = fmaf(a, s4.w, kk * xv.w);
+            if (wide) {
+                s4.x = (float)fma(ad, (double)s4.x, (double)kk * (double)xv.x);
+                s4.y = (float)fma(ad, (double)s4.y, (double)kk * (double)xv.y);
+                s4.z = (float)fma(ad, (double)s4.z, (double)kk * (double)xv.z);
+                s4.w = (float)fma(ad, (double)s4.w, (double)kk * (double)xv.w);
+            } else {
+                s4.x = fmaf(a, s4.x, kk * xv.x);
+                s4.y = fmaf(a, s4.y, kk * xv.y);
+                s4.z = fmaf(a, s4.z, kk * xv.z);
+                s4.w = fmaf(a, s4.w, kk * xv.w);
+            }
             *reinterpret_cast<float4*>(sp + (size_t)n * dv) = s4;
             y.x = fmaf(s4.x, qq, y.x);
             y.y = fmaf(s4.y, qq, y.y);
@@ -221,12 +260,13 @@ state_space_step_kernel(const float* __restrict__ q, const float* __restrict__ k
 // dt_raw [T, .] (rows ld_dt apart, head h at column h) with dt_bias, a_log [H]: the decay comes from the step size
 // as the header says; hpg: heads that share one head of q and k (1: each its own); skip [H] or null.
 // max_len > 0: requests that bring more tokens are left alone (the chunked kernel takes them).
+// wide_state: the state is held in double while a step's tokens are walked (see the kernel's header).
 extern "C" int aie_linear_recurrence(const float* q, const float* k, const float* v, int ld, const float* decay_tok,
                                      int ld_decay, const float* decay_head, float q_scale, float k_scale, float* state,
                                      float* out, const int* q_start, const int* q_len, const int* slots, int T, int R,
                                      int H, int d, int dv, int max_slots, unsigned* err, int hpg, const float* dt_raw,
                                      int ld_dt, const float* dt_bias, const float* a_log, const float* skip, int max_len,
-                                     cudaStream_t st) {
+                                     int wide_state, cudaStream_t st) {
     if (R <= 0) return 0;
     if (H <= 0 || d <= 0 || dv <= 0 || (!decay_tok && !decay_head && !dt_raw)) return AIE_BAD_ARG;
     if (hpg < 1 || H % hpg || (dt_raw && (!dt_bias || !a_log || decay_tok))) return AIE_BAD_ARG;
@@ -239,7 +279,7 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
         if (smem <= 48 * 1024 && (long long)R * H <= 0x7fffffffLL) {
             state_space_step_kernel<<<(unsigned)(R * H), SS_THREADS, smem, st>>>(q, k, v, ld, dt_raw, ld_dt, dt_bias, a_log, skip,
                                                                                  state, out, q_start, slots, H, d, dv, hpg,
-                                                                                 max_slots, err);
+                                                                                 max_slots, wide_state, err);
             AIE_LAUNCH_CHECK();
         }
     }
@@ -255,18 +295,27 @@ extern "C" int aie_linear_recurrence(const float* q, const float* k, const float
     if (blocks > 0x7fffffffLL) return AIE_UNSUPPORTED;
     int TT = 3072 / d;      // at most 36 KB of staged queries, keys and decays
     TT = TT < 1 ? 1 : (TT > LR_TOKENS ? LR_TOKENS : TT);
-    const size_t smem = ((size_t)TT * d * (decay_tok ? 3 : 2) + (size_t)TT * CB + 2 * TT) * sizeof(float);
+    const size_t smem = ((size_t)TT * d * (decay_tok ? 3 : 2) + (size_t)TT * CB + 3 * TT) * sizeof(float);
     // rows of the staged tokens are read as float4: the head's width and every thread's first row are multiples of 4
     const int vec = d % 4 == 0 ? 1 : 0;
     // ... and the rows in memory too when the row strides and base addresses allow 16-byte loads
     const int vec4 = (vec && ld % 4 == 0 && !((size_t)q & 15) && !((size_t)k & 15) &&
                       (!decay_tok || (ld_decay % 4 == 0 && !((size_t)decay_tok & 15)))) ? 1 : 0;
 #define GO(N)                                                                                                       \
-    linear_recurrence_kernel<N><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
+    do {                                                                                                            \
+    if (wide_state)                                                                                                 \
+        linear_recurrence_kernel<N, double><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
                                                                      q_scale, k_scale, state, out, q_start, q_len,  \
                                                                      slots, H, d, dv, lanes, groups, TT, max_slots, \
                                                                      vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
-                                                                     a_log, skip, max_len)
+                                                                     a_log, skip, max_len);                         \
+    else                                                                                                            \
+        linear_recurrence_kernel<N, float><<<(unsigned)blocks, LR_THREADS, smem, st>>>(q, k, v, ld, decay_tok, ld_decay, decay_head,  \
+                                                                     q_scale, k_scale, state, out, q_start, q_len,  \
+                                                                     slots, H, d, dv, lanes, groups, TT, max_slots, \
+                                                                     vec, vec4, err, hpg, dt_raw, ld_dt, dt_bias,   \
+                                                                     a_log, skip, max_len);                         \
+    } while (0)
     if (rpt == 4) GO(4);
     else if (rpt == 8) GO(8);
     else if (rpt == 16) GO(16);

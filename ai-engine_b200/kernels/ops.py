@@ -830,7 +830,7 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                       decay_head: Optional[torch.Tensor], q_scale: float, k_scale: float, state: torch.Tensor,
                       ctx, H: int, d: int, dv: int, heads_per_group: int = 1, dt_raw: Optional[torch.Tensor] = None,
                       dt_bias: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
-                      skip: Optional[torch.Tensor] = None, chunked: bool = False) -> torch.Tensor:
+                      skip: Optional[torch.Tensor] = None, chunked: bool = False, wide_state: bool = False) -> torch.Tensor:
     """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t per request and head over the step's tokens, the state
     [max_seqs, H, d, dv] float32 read and left in each request's slot.  q, k [T, H * d] and v [T, H * dv] are
     float32 views with one row stride; decay_tok [T, H * d] float32 (rows any stride) or decay_head [H].
@@ -839,6 +839,8 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
     heads_per_group: neighbouring heads that share one head of q and k ([T, H / heads_per_group * d]).
     skip [H]: skip[h] * v is added to the output.  chunked (with dt_raw): portions of SSD_MIN_TOKENS tokens or more
     take the chunked tensor-core kernel, which rounds q, k and v to bfloat16 (a state of up to 128 rows).
+    wide_state (with dt_raw): step sizes, decays and a step's updates are made in double and the state is rounded
+    once, when it returns to its float32 slot.
     Returns o [T, H, dv] float32."""
     _dev(state, decay_head, dt_bias, a_log, skip)
     if dt_raw is not None and (dt_raw.dtype != torch.float32 or dt_raw.stride(1) != 1 or dt_bias is None or a_log is None):
@@ -871,7 +873,8 @@ def linear_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_t
                                         _p(ctx.q_len), _p(ctx.slots), c_int(T), c_int(ctx.R), c_int(H), c_int(d), c_int(dv),
                                         c_int(state.shape[0]), _p(ctx.err), c_int(heads_per_group), _p(dt_raw),
                                         c_int(dt_raw.stride(0) if dt_raw is not None else 0), _p(dt_bias), _p(a_log),
-                                        _p(skip), c_int(max_len), _stream()), "linear_recurrence")
+                                        _p(skip), c_int(max_len), c_int(1 if wide_state else 0), _stream()),
+              "linear_recurrence")
     return out
 
 

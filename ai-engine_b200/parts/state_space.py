@@ -80,6 +80,7 @@ class ScalarDecayStateSpace(Mixer):
         y = ops.linear_recurrence(xbc[:, inner + GN:], xbc[:, inner:inner + GN], xbc[:, :inner], None, None, 1.0, 1.0,
                                   cache.state["S"], ctx, self.P, self.N, self.dv, heads_per_group=self.P // self.G,
                                   dt_raw=proj[:, inner + self.channels:], dt_bias=self.dt_bias, a_log=self.a_log,
-                                  skip=self.skip, chunked=self.env.dtype == torch.bfloat16)
+                                  skip=self.skip, chunked=self.env.dtype == torch.bfloat16,
+                                  wide_state=self.env.dtype == torch.float32)
         g = ops.gate_group_norm(y.view(-1, inner), proj[:, :inner], self.norm_w, self.norm_groups, self.eps, self.env.dtype)
         return ops.linear_parts(g, self.w_o, ctx.err)

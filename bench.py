@@ -73,16 +73,16 @@ def pifutar_shape(width, layers=8):
 
 def zupitar_shape(width, layers=8):
     """A Zupitar configuration with layers of the sizes real models of its kind have: attention heads of 128 (a quarter
-    of them key heads, half of each head rotated, three taps behind the projections) beside a state-space mixer as wide
+    of them key heads, half of each head rotated, four taps behind the projections) beside a state-space mixer as wide
     as the model (heads of 64, a state of 128, eight groups); state-space layers on their own twice as wide; a dense
     feed-forward of 3 x width or 30 experts of width / 2 and two identity experts (top 4, two of four groups kept);
     the pattern of six layers (parallel dense, state-space experts, parallel dense, parallel experts, parallel dense,
     state-space experts) repeats."""
     H = width // 128
     ssm = lambda inner, taps: dict(heads=inner // 64, vdim=64, state=128, groups=8, conv=taps, norm_groups=8)
-    par = dict(left=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, conv=3, scale=128 ** -0.5,
-                         rot=dict(base=250000.0, dims=64, scaling=dict(factor=4.0))),
-               right=ssm(width, 3), left_scale=0.8, right_scale=1.1)
+    par = dict(left=dict(heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, conv=4, scale=128 ** -0.5,
+                         rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0))),
+               right=ssm(width, 4), left_scale=0.7, right_scale=1.2)
     moe = dict(kind="moe", expert=dict(ff=width // 2), router=dict(experts=30, identity=2, top=4, groups=dict(count=4, keep=2)))
     dense = dict(kind="dense", ff=3 * width)
     out = []

@@ -215,6 +215,26 @@ def test_state_space_mixer_in_portions_decoding_and_on_a_slot_used_again(dtype, 
     assert (got[0] - refs[2]).abs().max() <= tol(dtype, refs[2], 3e-5, 6e-2)
 
 
+def test_a_slow_constant_decay_keeps_its_digits_over_a_long_prompt():
+    """A head whose step size hardly changes and whose decay is near one (what carries a token a thousand places):
+    rounded to float32 such a decay repeats the same rounding at every token, and a far token's share drifts by
+    tokens x 3e-8.  The float32 engine works the decay out in double; whole, and with the last hundred decoded."""
+    D, P, dv, N, G, taps, ng = 24, 2, 8, 8, 1, 2, 1
+    g = torch.Generator().manual_seed(9)
+    t = ssm_tensors(g, D, P, dv, N, G, taps, torch.float32)
+    t["in"][2 * P * dv + 2 * G * N:] = 0.0                # the step size is its bias alone
+    t["dt_bias"] = torch.tensor([-6.0, -5.0])             # dt = 0.0025, 0.0067
+    t["A_log"] = torch.tensor([0.0, -0.5])                # decays 0.9975 and 0.9959 a token
+    part = load(ssm_part(torch.float32, D, P, dv, N, G, taps, ng, 1e-5), t, torch.float32)
+    n = 1500
+    x = torch.randn(n, D, generator=g)
+    ref = ssm_oracle(x, t, P, dv, N, G, taps, ng, 1e-5, torch.float64).double()
+    for cuts in ([n], [n - 100] + [1] * 100):
+        got = Rig(part, torch.float32, max_seqs=1).run([x], [cuts])[0]
+        err = (got[-100:] - ref[-100:]).abs().max() / ref[-100:].abs().max()
+        assert float(err) <= 4e-6, (cuts[:2], float(err))
+
+
 def test_state_space_decay_and_step_size_by_hand():
     """One head of two channels and one state row: the recurrence in closed form.  The convolution's weight is zero,
     so x, B and C are constants (silu of the bias), and dt and the decay follow from dt_bias and A_log alone."""

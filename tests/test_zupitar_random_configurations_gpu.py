@@ -37,7 +37,7 @@ def draw(seed):
                  scale=float(dim ** -0.5 * pick([1.0, 0.6, 1.5])))
         r = rng.rand()
         if r < 0.8:
-            m["rot"] = dict(base=float(pick([100.0, 10000.0, 250000.0])), dims=int(pick([dim, dim // 2, 8])))
+            m["rot"] = dict(base=float(pick([100.0, 10000.0, 200000.0])), dims=int(pick([dim, dim // 2, 8])))
             if rng.rand() < 0.6:
                 m["rot"]["scaling"] = dict(factor=float(pick([2.0, 4.0, 1.5])))
         return m
@@ -63,13 +63,13 @@ def draw(seed):
             mlp = dict(kind="moe", expert=dict(ff=int(pick([8, 30, 64, 128]))), router=router)
         if rng.rand() < 0.6:
             layers.append(dict(type="parallel", mlp=mlp, mixer=dict(
-                left=attn(), right=ssm(), left_scale=float(pick([1.0, 0.8, 0.5, 1.4])), right_scale=float(pick([1.0, 1.1, 0.3])))))
+                left=attn(), right=ssm(), left_scale=float(pick([1.0, 0.75, 0.5, 1.4])), right_scale=float(pick([1.0, 1.2, 0.3])))))
         else:
             layers.append(dict(type="mamba2", mixer=ssm(), mlp=mlp))
     raw = dict(architecture="Zupitar", vocab=int(rng.randint(50, 400)), width=width,
                norm=dict(eps=float(pick([1e-6, 1e-5, 1e-3]))), layers=layers)
     if rng.rand() < 0.7:
-        raw["logit_softcap"] = float(pick([5.0, 15.0, 30.0]))
+        raw["logit_softcap"] = float(pick([5.0, 12.0, 30.0]))
     return raw
 
 
